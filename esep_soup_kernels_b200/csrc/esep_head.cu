@@ -8,12 +8,15 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <atomic>
+#include <cstring>
 #include <mutex>
 
 #include "head_aux.cuh"
 #include "head_bwd.cuh"
 #include "head_fwd.cuh"
 #include "head_norm.cuh"
+#include "head_step.cuh"
 #include "head_train.cuh"
 
 using namespace esep;
@@ -29,10 +32,14 @@ struct DeviceInfo {
   int init_status = ESEP_ERR_CUDA;
 };
 
-std::once_flag g_once[kMaxDevices];
+// Per-device init-once table. `g_ready` is set only when the initialisation reached a final
+// verdict (ok, or a device that can never run the kernels); a transient CUDA failure leaves it
+// clear, so the next call tries again instead of failing for the life of the process.
+std::mutex g_init_mutex;
+std::atomic<int> g_ready[kMaxDevices];
 DeviceInfo g_info[kMaxDevices];
 PFN_cuTensorMapEncodeTiled g_encode = nullptr;
-std::once_flag g_encode_once;
+std::atomic<long long> g_init_calls{0};   // completed per-device initialisations (test aid)
 
 size_t align_up(size_t x) { return (x + kAlign - 1) / kAlign * kAlign; }
 
@@ -54,25 +61,27 @@ cudaError_t set_smem(K kernel, int bytes) {
   return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
 }
 
-void init_device(int device) {
-  DeviceInfo& d = g_info[device];
+// Runs under g_init_mutex. Returns true when the verdict in g_info[device] is final.
+bool init_device(int device) {
+  DeviceInfo d;
   int prev = -1;
-  if (cudaGetDevice(&prev) != cudaSuccess) return;
-  if (cudaSetDevice(device) != cudaSuccess) return;
+  if (cudaGetDevice(&prev) != cudaSuccess) return false;
+  if (cudaSetDevice(device) != cudaSuccess) return false;
   cudaDeviceProp prop;
   if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) {
     cudaSetDevice(prev);
-    return;
+    return false;
   }
   d.cc_major = prop.major;
   d.cc_minor = prop.minor;
   d.sm_count = prop.multiProcessorCount;
   if (prop.major != 10) {
     d.init_status = ESEP_ERR_UNSUPPORTED_ARCH;
+    g_info[device] = d;
     cudaSetDevice(prev);
-    return;
+    return true;
   }
-  std::call_once(g_encode_once, load_encode);
+  if (g_encode == nullptr) load_encode();
   bool ok = g_encode != nullptr;
   ok = ok && set_smem(head_fwd_kernel<0>, fwd::SMEM_BYTES) == cudaSuccess;
   ok = ok && set_smem(head_fwd_kernel<1>, fwd::SMEM_BYTES) == cudaSuccess;
@@ -122,13 +131,27 @@ void init_device(int device) {
       ok = false;
   }
   cudaGetLastError();
-  d.init_status = ok ? ESEP_OK : ESEP_ERR_CUDA;
   cudaSetDevice(prev);
+  if (!ok) return false;
+  d.init_status = ESEP_OK;
+  g_info[device] = d;
+  return true;
 }
 
 int device_info(int device, const DeviceInfo** out) {
   if (device < 0 || device >= kMaxDevices) return ESEP_ERR_BAD_ARG;
-  std::call_once(g_once[device], init_device, device);
+  if (g_ready[device].load(std::memory_order_acquire) == 0) {
+    std::lock_guard<std::mutex> lock(g_init_mutex);
+    if (g_ready[device].load(std::memory_order_relaxed) == 0) {
+      if (!init_device(device)) {
+        cudaGetLastError();
+        *out = nullptr;
+        return ESEP_ERR_CUDA;   // nothing is remembered: the next call tries again
+      }
+      g_init_calls.fetch_add(1);
+      g_ready[device].store(1, std::memory_order_release);
+    }
+  }
   *out = &g_info[device];
   return g_info[device].init_status;
 }
@@ -142,10 +165,62 @@ int current_device_info(const DeviceInfo** out) {
   return device_info(dev, out);
 }
 
+// Encoded tensor maps are kept in a small table keyed on everything that goes into them (the
+// counterpart of the reference's per-weight cache, solution/head/patch.py:93-101: the head weight
+// and the library's own buffers keep their addresses from step to step). A map is address
+// arithmetic only, so an entry can never go stale: the same key always encodes the same map.
+struct TmapKey {
+  const void* ptr;
+  uint64_t rows, cols;
+  uint32_t box[3];
+  int dtype, dims;
+  bool operator==(const TmapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && box[0] == o.box[0] &&
+           box[1] == o.box[1] && box[2] == o.box[2] && dtype == o.dtype && dims == o.dims;
+  }
+};
+constexpr int kTmapSlots = 64;
+std::mutex g_tmap_mutex;
+TmapKey g_tmap_keys[kTmapSlots];
+CUtensorMap g_tmap_vals[kTmapSlots];
+int g_tmap_used = 0, g_tmap_next = 0;
+std::atomic<long long> g_tmap_encodes{0};
+
+bool tmap_lookup(const TmapKey& key, CUtensorMap* map) {
+  std::lock_guard<std::mutex> lock(g_tmap_mutex);
+  for (int i = 0; i < g_tmap_used; ++i)
+    if (g_tmap_keys[i] == key) {
+      *map = g_tmap_vals[i];
+      return true;
+    }
+  return false;
+}
+void tmap_store(const TmapKey& key, const CUtensorMap& map) {
+  std::lock_guard<std::mutex> lock(g_tmap_mutex);
+  const int slot = g_tmap_used < kTmapSlots ? g_tmap_used++ : (g_tmap_next++ % kTmapSlots);
+  g_tmap_keys[slot] = key;
+  g_tmap_vals[slot] = map;
+}
+
+int make_tmap_uncached(CUtensorMap* map, const void* ptr, int dtype, uint64_t rows, uint64_t cols,
+                       uint32_t box_cols, uint32_t box_rows);
+int make_tmap_w3_uncached(CUtensorMap* map, const void* ptr, int dtype, uint64_t rows,
+                          uint64_t cols, uint32_t box_rows, uint32_t box_blocks);
+
 // 2-D row-major 16-bit tensor [rows, cols], box {box_cols, box_rows}, 128-byte swizzle,
 // out-of-bounds elements read as zero.
 int make_tmap(CUtensorMap* map, const void* ptr, int dtype, uint64_t rows, uint64_t cols,
               uint32_t box_cols, uint32_t box_rows) {
+  const TmapKey key = {ptr, rows, cols, {box_cols, box_rows, 0}, dtype, 2};
+  if (tmap_lookup(key, map)) return ESEP_OK;
+  const int st = make_tmap_uncached(map, ptr, dtype, rows, cols, box_cols, box_rows);
+  if (st == ESEP_OK) tmap_store(key, *map);
+  return st;
+}
+
+int make_tmap_uncached(CUtensorMap* map, const void* ptr, int dtype, uint64_t rows, uint64_t cols,
+                       uint32_t box_cols, uint32_t box_rows) {
+  g_tmap_encodes.fetch_add(1);
   const cuuint64_t gdim[2] = {cols, rows};
   const cuuint64_t gstride[1] = {cols * 2};
   const cuuint32_t box[2] = {box_cols, box_rows};
@@ -163,6 +238,16 @@ int make_tmap(CUtensorMap* map, const void* ptr, int dtype, uint64_t rows, uint6
 // shared memory as box_blocks consecutive 64-wide tiles of box_rows lines.
 int make_tmap_w3(CUtensorMap* map, const void* ptr, int dtype, uint64_t rows, uint64_t cols,
                  uint32_t box_rows, uint32_t box_blocks) {
+  const TmapKey key = {ptr, rows, cols, {64, box_rows, box_blocks}, dtype, 3};
+  if (tmap_lookup(key, map)) return ESEP_OK;
+  const int st = make_tmap_w3_uncached(map, ptr, dtype, rows, cols, box_rows, box_blocks);
+  if (st == ESEP_OK) tmap_store(key, *map);
+  return st;
+}
+
+int make_tmap_w3_uncached(CUtensorMap* map, const void* ptr, int dtype, uint64_t rows,
+                          uint64_t cols, uint32_t box_rows, uint32_t box_blocks) {
+  g_tmap_encodes.fetch_add(1);
   const cuuint64_t gdim[3] = {64, rows, cols / 64};
   const cuuint64_t gstride[2] = {cols * 2, 128};
   const cuuint32_t box[3] = {64, box_rows, box_blocks};
@@ -212,7 +297,11 @@ int esep_head_query(int device, esep_head_caps* caps) {
   if (caps == nullptr) return ESEP_ERR_BAD_ARG;
   const DeviceInfo* d = nullptr;
   const int st = device_info(device, &d);
-  if (d == nullptr) return st;
+  if (d == nullptr) {
+    caps->cc_major = caps->cc_minor = caps->sm_count = caps->max_clusters_bwd = 0;
+    caps->supported = 0;
+    return st;
+  }
   caps->cc_major = d->cc_major;
   caps->cc_minor = d->cc_minor;
   caps->sm_count = d->sm_count;
@@ -274,15 +363,11 @@ int esep_head_plan_problem(int64_t n, int64_t h, int64_t v_local, int need_grad,
     const int ncl = static_cast<int>(std::min<int64_t>(
         std::max(1, max_clusters_bwd), n_tp * pl.bwd_total_steps));
     pl.bwd_grid = ncl * kBwdCluster;
-    pl.bwd_full_rounds = static_cast<int>(n_tp / ncl);
-    pl.bwd_rem_pairs = static_cast<int>(n_tp - static_cast<int64_t>(pl.bwd_full_rounds) * ncl);
-    pl.bwd_rem_splits = 0;
-    pl.bwd_steps_per_split = 0;
-    if (pl.bwd_rem_pairs > 0) {
-      const int want = std::min(ncl / pl.bwd_rem_pairs, pl.bwd_total_steps);
-      pl.bwd_steps_per_split = div_up(pl.bwd_total_steps, want);
-      pl.bwd_rem_splits = div_up(pl.bwd_total_steps, pl.bwd_steps_per_split);
-    }
+    const SweepSplit sp = sweep_split(n_tp, ncl, pl.bwd_total_steps);
+    pl.bwd_full_rounds = sp.full_rounds;
+    pl.bwd_rem_pairs = sp.rem_tp;
+    pl.bwd_rem_splits = sp.rem_splits;
+    pl.bwd_steps_per_split = sp.steps_per_split;
   }
   // ---- workspace -------------------------------------------------------------------------
   size_t off = 0;
@@ -360,6 +445,8 @@ int esep_head_forward_partial(const void* x, const void* w, const int64_t* targe
   p.pidx = reinterpret_cast<int*>(part + 4 * pn);
   p.status = status;
   p.gate = g_gate;
+  p.row_range = nullptr;
+  p.part_cap = 0;
 
   {
     // The kernel strides its work units by the number of launched pairs, so clamping the grid
@@ -571,14 +658,19 @@ namespace {
 // 16 MiB until the process exits. In host code the symbol below is only a handle; its device
 // address is looked up once per device with cudaGetSymbolAddress.
 static __device__ __align__(256) unsigned char g_static_scratch[ESEP_STATIC_SCRATCH_BYTES];
-std::once_flag g_static_once[kMaxDevices];
+std::mutex g_static_mutex;
 void* g_static_ptr[kMaxDevices] = {};
 
-void resolve_static_scratch(int device) {
-  // Runs with `device` current (the caller checked). No allocation happens here.
-  void* ptr = nullptr;
-  if (cudaGetSymbolAddress(&ptr, g_static_scratch) == cudaSuccess) g_static_ptr[device] = ptr;
-  else cudaGetLastError();
+// Device address of the scratch array on `device`, which must be current. Looked up once per
+// device; a failed lookup is not remembered, so a later call can try again. No allocation.
+void* resolve_static_scratch(int device) {
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (g_static_ptr[device] == nullptr) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_static_scratch) == cudaSuccess) g_static_ptr[device] = ptr;
+    else cudaGetLastError();
+  }
+  return g_static_ptr[device];
 }
 }  // namespace
 
@@ -602,8 +694,7 @@ int esep_head_forward_static(const void* x, const void* w, const int64_t* target
   if (pl.ws_bytes > ESEP_STATIC_SCRATCH_BYTES) return ESEP_ERR_STATIC_SCRATCH;
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return ESEP_ERR_CUDA;
-  std::call_once(g_static_once[dev], resolve_static_scratch, dev);
-  void* scratch = g_static_ptr[dev];
+  void* scratch = resolve_static_scratch(dev);
   if (scratch == nullptr) return ESEP_ERR_CUDA;
   // The forward clears the status word itself; every other scratch cell it reads is written
   // earlier in the same call, so nothing else has to start at zero.
@@ -713,49 +804,380 @@ int esep_head_norm_backward(const float* dy, const float* r_out, const float* rs
 }  // extern "C"
 
 
+
+
 // ---------------------------------------------------------------------------------------------
-// Single-sweep training call: statistics and dHidden from one pass over the vocabulary
-// (head_train.cuh). Workspace = the regular plan's workspace followed by the sweep's own arrays.
+// Whole head step: row classes decided on the device, one pass over the vocabulary for the rows
+// that need a gradient (head_train.cuh), a forward sweep for the rest, outputs in the caller's
+// row order (head_step.cuh). Workspace = the regular plan's workspace (used by the host-planned
+// prefix sweep and by the guarded two-kernel pass) followed by the step's own arrays.
 // ---------------------------------------------------------------------------------------------
 namespace {
 constexpr int64_t kPrefixRows = 2048;   // vocabulary prefix that gives the per-row reference maximum
 
-struct TrainLayout {
-  esep_head_plan pl;
-  size_t base_bytes, record_off, st_off, lo_off, flag_off, total;
-  size_t st_elems, lo_elems;
+struct StepLayout {
+  esep_head_plan pl;   // host plan for all m rows with gradient
+  int ncl;             // clusters of the training sweep launch
+  int part_cap;        // rows of the forward partial arrays
+  size_t base_bytes;
+  size_t record_off, st_off, st_stride, lo_off, lo_stride, dxpart_off, xc_off, tgtc_off, tgto_off,
+      cewc_off, perm_off, inv_off, dxc_off, part_off, part_stride, fb_off, fb_stride, fbam_off,
+      floss_off, total;
 };
 
-int train_layout(int64_t n, int64_t h, int64_t v, const DeviceInfo* d, TrainLayout* t) {
-  int st = esep_head_plan_problem(n, h, v, 1, d->sm_count, d->max_clusters_bwd, &t->pl);
+int step_layout(int64_t m, int64_t h, int64_t v, bool need_grad, const DeviceInfo* d,
+                StepLayout* t) {
+  int st = esep_head_plan_problem(m, h, v, 1, d->sm_count, d->max_clusters_bwd, &t->pl);
   if (st != ESEP_OK) return st;
   esep_head_plan pre;
-  st = esep_head_plan_problem(n, h, std::min<int64_t>(v, kPrefixRows), 0, d->sm_count,
+  st = esep_head_plan_problem(m, h, std::min<int64_t>(v, kPrefixRows), 0, d->sm_count,
                               d->max_clusters_bwd, &pre);
   if (st != ESEP_OK) return st;
-  t->base_bytes = align_up(std::max(t->pl.ws_bytes, pre.ws_bytes));
-  t->record_off = t->base_bytes;
-  t->st_off = t->record_off + align_up(static_cast<size_t>(5) * n * sizeof(float));
-  t->st_elems = static_cast<size_t>(16) * n;
-  t->lo_off = t->st_off + 4 * align_up(t->st_elems * sizeof(float));
-  t->lo_elems = static_cast<size_t>(std::max(t->pl.bwd_rem_splits, 0)) * 16 *
-                static_cast<size_t>(t->pl.bwd_rem_pairs) * 128;
-  t->flag_off = t->lo_off + 4 * align_up(t->lo_elems * sizeof(float));
-  t->total = t->flag_off + kAlign;
+  const esep_head_plan& pl = t->pl;
+  t->ncl = pl.bwd_grid / kBwdCluster;
+  const size_t mr = static_cast<size_t>(div_up(m, 256)) * 256;
+  t->part_cap = static_cast<int>(std::min<size_t>(mr + static_cast<size_t>(4) * 256 * d->max_pairs_fwd,
+                                                  static_cast<size_t>(1) << 30));
+  const size_t f4 = sizeof(float);
+  size_t off = align_up(std::max(pl.ws_bytes, pre.ws_bytes));
+  t->base_bytes = off;
+  auto take = [&](size_t bytes) {
+    const size_t at = off;
+    off += align_up(bytes);
+    return at;
+  };
+  t->tgto_off = take(static_cast<size_t>(m) * 8);
+  t->tgtc_off = take(static_cast<size_t>(m) * 8);
+  t->cewc_off = take(static_cast<size_t>(m) * f4);
+  t->perm_off = take(static_cast<size_t>(m) * 4);
+  t->inv_off = take(static_cast<size_t>(m) * 4);
+  t->xc_off = take(static_cast<size_t>(m) * h * 2);
+  t->part_stride = align_up(static_cast<size_t>(t->part_cap) * f4);
+  t->part_off = take(5 * t->part_stride);
+  // what only a call with gradient needs
+  t->record_off = off;
+  t->st_off = t->lo_off = t->dxpart_off = t->dxc_off = t->fb_off = t->fbam_off = t->floss_off = off;
+  t->st_stride = t->lo_stride = t->fb_stride = 0;
+  if (need_grad) {
+    t->record_off = take(static_cast<size_t>(ESEP_RECORD_FIELDS) * m * f4);
+    t->st_stride = align_up(static_cast<size_t>(16) * m * f4);
+    t->st_off = take(4 * t->st_stride);
+    // a left-over pair is cut into at most ncl / rem_tp runs: rem_tp * rem_splits <= ncl
+    t->lo_stride = align_up(static_cast<size_t>(16) * 128 * t->ncl * f4);
+    t->lo_off = take(4 * t->lo_stride);
+    t->dxpart_off = take(static_cast<size_t>(t->ncl) * 128 * kBwdCluster * pl.bwd_hslice * f4);
+    t->dxc_off = take(static_cast<size_t>(m) * h * f4);
+    t->fb_stride = align_up(static_cast<size_t>(m) * f4);
+    t->fb_off = take(5 * t->fb_stride);
+    t->fbam_off = take(static_cast<size_t>(m) * 8);
+    t->floss_off = take(kAlign);
+  }
+  t->total = off;
+  return ESEP_OK;
+}
+
+struct StepArgs {
+  const void* x;
+  int x_dtype;               // ESEP_DTYPE_F16 / BF16 (= dtype) or ESEP_DTYPE_F32
+  const void* w;
+  const void* w_bf16;        // bf16 copy of W for the dHidden GEMM (w itself for bf16 models)
+  int dtype;
+  int64_t m, h, v;
+  const int64_t* target;     // flat rows
+  const float* ce_weight;
+  const int64_t* labels;     // or a [batch, seq_len] step
+  const int64_t* attention_mask;
+  int64_t seq_len;
+  int need_grad;
+  float *lse, *target_logit, *ce, *entropy, *cew_out, *loss, *metrics, *dx;
+  int64_t* argmax;
+  int* overflow;             // may be null
+  void* workspace;
+  size_t workspace_bytes;
+  void* stream;
+};
+
+template <typename K, typename... A>
+int launch_cluster(K kernel, unsigned grid, unsigned block, size_t smem, unsigned cluster,
+                   cudaStream_t s, A... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(block);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = cluster;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kernel, args...) != cudaSuccess) {
+    cudaGetLastError();
+    return ESEP_ERR_CUDA;
+  }
+  return ESEP_OK;
+}
+
+int step_impl(const StepArgs& a) {
+  int st = check_problem(a.x, a.w, a.m, a.h, a.v, a.dtype);
+  if (st != ESEP_OK) return st;
+  const bool step_mode = a.labels != nullptr;
+  if (!step_mode && a.target == nullptr) return ESEP_ERR_BAD_ARG;
+  if (step_mode && (a.seq_len <= 0 || a.m % a.seq_len != 0)) return ESEP_ERR_BAD_ARG;
+  if (a.x_dtype != a.dtype && a.x_dtype != ESEP_DTYPE_F32) return ESEP_ERR_BAD_ARG;
+  if (a.lse == nullptr || a.target_logit == nullptr || a.ce == nullptr || a.entropy == nullptr ||
+      a.argmax == nullptr || a.cew_out == nullptr || a.loss == nullptr)
+    return ESEP_ERR_BAD_ARG;
+  const bool need_grad = a.need_grad != 0;
+  if (need_grad) {
+    if (a.dx == nullptr || a.w_bf16 == nullptr) return ESEP_ERR_BAD_ARG;
+    if ((reinterpret_cast<uintptr_t>(a.dx) & 15u) || (reinterpret_cast<uintptr_t>(a.w_bf16) & 15u))
+      return ESEP_ERR_ALIGNMENT;
+  }
+  const DeviceInfo* d = nullptr;
+  st = current_device_info(&d);
+  if (st != ESEP_OK) return st;
+  StepLayout t;
+  st = step_layout(a.m, a.h, a.v, need_grad, d, &t);
+  if (st != ESEP_OK) return st;
+  if (a.workspace == nullptr || (reinterpret_cast<uintptr_t>(a.workspace) & (kAlign - 1)) ||
+      a.workspace_bytes < t.total)
+    return ESEP_ERR_WORKSPACE;
+  cudaStream_t s = static_cast<cudaStream_t>(a.stream);
+  uint8_t* ws = static_cast<uint8_t*>(a.workspace);
+  const esep_head_plan& pl = t.pl;
+  const int m = static_cast<int>(a.m), h = static_cast<int>(a.h), v = static_cast<int>(a.v);
+  int* status = reinterpret_cast<int*>(ws + pl.ws_status_off);
+  int* counts = reinterpret_cast<int*>(ws + 64);          // inside the status block
+  int* overflow = a.overflow != nullptr ? a.overflow : reinterpret_cast<int*>(ws + 96);
+  long long* tgt_o = reinterpret_cast<long long*>(ws + t.tgto_off);
+  long long* tgt_c = reinterpret_cast<long long*>(ws + t.tgtc_off);
+  float* cew_c = reinterpret_cast<float*>(ws + t.cewc_off);
+  int* perm = reinterpret_cast<int*>(ws + t.perm_off);
+  int* inv = reinterpret_cast<int*>(ws + t.inv_off);
+  void* xc = ws + t.xc_off;
+  float* part = reinterpret_cast<float*>(ws + t.part_off);
+  float* record = reinterpret_cast<float*>(ws + t.record_off);
+  float* dxc = reinterpret_cast<float*>(ws + t.dxc_off);
+
+  // 1. row classes, compact order, counts (device only)
+  StepPrepParams q = {};
+  q.m = m;
+  q.v = v;
+  q.seq_len = static_cast<int>(step_mode ? a.seq_len : 1);
+  q.need_grad = need_grad ? 1 : 0;
+  q.target = reinterpret_cast<const long long*>(a.target);
+  q.ce_weight = a.ce_weight;
+  q.labels = reinterpret_cast<const long long*>(a.labels);
+  q.attn = reinterpret_cast<const long long*>(a.attention_mask);
+  q.tgt_o = tgt_o;
+  q.tgt_c = tgt_c;
+  q.cew_c = cew_c;
+  q.perm = perm;
+  q.inv = inv;
+  q.counts = counts;
+  q.overflow = overflow;
+  q.status = status;
+  head_step_prep_kernel<<<1, 1024, 0, s>>>(q);
+  if (cudaGetLastError() != cudaSuccess) return ESEP_ERR_CUDA;
+
+  // 2. compact 16-bit copy of the selected rows
+  {
+    const bool f32 = a.x_dtype == ESEP_DTYPE_F32;
+    const unsigned grid = static_cast<unsigned>(m);
+    if (a.dtype == ESEP_DTYPE_F16) {
+      if (f32) head_step_gather_kernel<0, true><<<grid, 128, 0, s>>>(a.x, perm, h, xc);
+      else head_step_gather_kernel<0, false><<<grid, 128, 0, s>>>(a.x, perm, h, xc);
+    } else {
+      if (f32) head_step_gather_kernel<1, true><<<grid, 128, 0, s>>>(a.x, perm, h, xc);
+      else head_step_gather_kernel<1, false><<<grid, 128, 0, s>>>(a.x, perm, h, xc);
+    }
+    if (cudaGetLastError() != cudaSuccess) return ESEP_ERR_CUDA;
+  }
+
+  const size_t st_stride = t.st_stride, lo_stride = t.lo_stride;
+  TrainParams p = {};
+  if (need_grad) {
+    // 3. reference maximum per row: the forward sweep over a vocabulary prefix (record field 0).
+    //    Host-planned over all m compact rows; the rows past n_sel hold zeros.
+    g_gate = nullptr;
+    st = esep_head_forward_partial(xc, a.w, reinterpret_cast<const int64_t*>(tgt_c), a.m, a.h,
+                                   std::min<int64_t>(a.v, kPrefixRows), 0, a.dtype, record,
+                                   a.workspace, t.base_bytes, a.stream);
+    if (st != ESEP_OK) return st;
+
+    // 4. the training sweep over the compact rows [0, n_sweep)
+    CUtensorMap tx, tw1, tw2;
+    if (make_tmap(&tx, xc, a.dtype, a.m, a.h, bwd::BK, 64) != ESEP_OK) return ESEP_ERR_CUDA;
+    if (make_tmap(&tw1, a.w, a.dtype, a.v, a.h, bwd::BK, bwd::BV) != ESEP_OK) return ESEP_ERR_CUDA;
+    const bool w2_is_3d = (a.h % 64 == 0);
+    if (w2_is_3d) {
+      if (make_tmap_w3(&tw2, a.w_bf16, ESEP_DTYPE_BF16, a.v, a.h, bwd::G2_KV, 6) != ESEP_OK)
+        return ESEP_ERR_CUDA;
+    } else if (make_tmap(&tw2, a.w_bf16, ESEP_DTYPE_BF16, a.v, a.h, 64, bwd::G2_KV) != ESEP_OK) {
+      return ESEP_ERR_CUDA;
+    }
+    p.n = m;
+    p.h = h;
+    p.v = v;
+    p.n_dev = counts + CNT_SWEEP;
+    p.nhb = pl.bwd_hblocks;
+    p.total_steps = pl.bwd_total_steps;
+    p.m_ref = record;
+    p.target = tgt_c;
+    p.dx = dxc;
+    p.dx_part = reinterpret_cast<float*>(ws + t.dxpart_off);
+    p.st_s = reinterpret_cast<float*>(ws + t.st_off);
+    p.st_t = reinterpret_cast<float*>(ws + t.st_off + st_stride);
+    p.st_max = reinterpret_cast<float*>(ws + t.st_off + 2 * st_stride);
+    p.st_idx = reinterpret_cast<int*>(ws + t.st_off + 3 * st_stride);
+    p.lo_s = reinterpret_cast<float*>(ws + t.lo_off);
+    p.lo_t = reinterpret_cast<float*>(ws + t.lo_off + lo_stride);
+    p.lo_max = reinterpret_cast<float*>(ws + t.lo_off + 2 * lo_stride);
+    p.lo_idx = reinterpret_cast<int*>(ws + t.lo_off + 3 * lo_stride);
+    p.w2_is_3d = w2_is_3d ? 1 : 0;
+    p.overflow = overflow;
+    p.status = status;
+    st = a.dtype == ESEP_DTYPE_F16
+             ? launch_cluster(head_train_kernel<0>, static_cast<unsigned>(pl.bwd_grid),
+                              trn::THREADS_T, trn::SMEM_BYTES_T, kBwdCluster, s, tx, tw1, tw2, p)
+             : launch_cluster(head_train_kernel<1>, static_cast<unsigned>(pl.bwd_grid),
+                              trn::THREADS_T, trn::SMEM_BYTES_T, kBwdCluster, s, tx, tw1, tw2, p);
+    if (st != ESEP_OK) return st;
+  }
+
+  // 5. forward sweep over the compact rows [n_sweep, n_sel): statistics only
+  const unsigned fwd_grid = static_cast<unsigned>(2 * d->max_pairs_fwd);
+  FwdParams f = {};
+  {
+    CUtensorMap tx, tw;
+    if (make_tmap(&tx, xc, a.dtype, a.m, a.h, fwd::BK, fwd::BM) != ESEP_OK) return ESEP_ERR_CUDA;
+    if (make_tmap(&tw, a.w, a.dtype, a.v, a.h, fwd::BK, fwd::BN / 2) != ESEP_OK)
+      return ESEP_ERR_CUDA;
+    f.n = m;
+    f.h = h;
+    f.v = v;
+    f.n_row_tiles = pl.fwd_row_tiles;
+    f.n_row_pairs = div_up(pl.fwd_row_tiles, 2);
+    f.n_vtiles = pl.fwd_vocab_tiles;
+    f.tiles_per_unit = pl.fwd_tiles_per_unit;
+    f.n_splits = pl.fwd_splits;
+    f.vocab_offset = 0;
+    f.target = tgt_c;
+    const size_t ps = t.part_stride / sizeof(float);
+    f.pm = part;
+    f.ps = part + ps;
+    f.pt = part + 2 * ps;
+    f.ptz = part + 3 * ps;
+    f.pidx = reinterpret_cast<int*>(part + 4 * ps);
+    f.status = status;
+    f.gate = nullptr;
+    f.row_range = counts + CNT_SWEEP;   // {n_sweep, n_sel}
+    f.part_cap = t.part_cap;
+    st = a.dtype == ESEP_DTYPE_F16
+             ? launch_cluster(head_fwd_kernel<0>, fwd_grid, fwd::THREADS, fwd::SMEM_BYTES, 2, s, tx,
+                              tw, f)
+             : launch_cluster(head_fwd_kernel<1>, fwd_grid, fwd::THREADS, fwd::SMEM_BYTES, 2, s, tx,
+                              tw, f);
+    if (st != ESEP_OK) return st;
+  }
+
+  float* fb = reinterpret_cast<float*>(ws + t.fb_off);
+  const size_t fbs = t.fb_stride / sizeof(float);
+  long long* fb_amax = reinterpret_cast<long long*>(ws + t.fbam_off);
+  if (need_grad) {
+    // 6. guarded second attempt on the compact rows: the two-kernel path, enqueued behind the
+    //    overflow flag. Its kernels return at once unless a row overflowed in the sweep; if one
+    //    did, they leave per-row results and final dHidden rows in compact order.
+    g_gate = overflow;
+    st = esep_head_forward(xc, a.w, reinterpret_cast<const int64_t*>(tgt_c), cew_c, a.m, a.h, a.v,
+                           a.dtype, fb, fb + fbs, fb + 2 * fbs, fb + 3 * fbs,
+                           reinterpret_cast<int64_t*>(fb_amax), fb + 4 * fbs,
+                           reinterpret_cast<float*>(ws + t.floss_off), nullptr, a.workspace,
+                           t.base_bytes, a.stream);
+    if (st == ESEP_OK)
+      st = esep_head_backward(xc, a.w, reinterpret_cast<const int64_t*>(tgt_c), fb + 4 * fbs, fb,
+                              a.m, a.h, a.v, 0, a.dtype, dxc, a.workspace, t.base_bytes, a.stream);
+    g_gate = nullptr;
+    if (st != ESEP_OK) return st;
+  }
+
+  // 7. per-row finish in the caller's row order, 8. the scalars
+  StepRowsParams r = {};
+  r.m = m;
+  r.h = h;
+  r.v = v;
+  r.n_clusters = t.ncl;
+  r.nhb = pl.bwd_hblocks;
+  r.total_steps = pl.bwd_total_steps;
+  r.n_vtiles = pl.fwd_vocab_tiles;
+  r.fwd_pairs = static_cast<int>(fwd_grid / 2);
+  r.part_cap = t.part_cap;
+  r.counts = counts;
+  r.overflow = overflow;
+  r.inv = inv;
+  r.xc = xc;
+  r.w = a.w;
+  r.tgt_c = tgt_c;
+  r.cew_c = cew_c;
+  r.m_ref = record;
+  r.st_s = p.st_s; r.st_t = p.st_t; r.st_max = p.st_max; r.st_idx = p.st_idx;
+  r.lo_s = p.lo_s; r.lo_t = p.lo_t; r.lo_max = p.lo_max; r.lo_idx = p.lo_idx;
+  r.dx_part = p.dx_part;
+  r.dxc = dxc;
+  r.pm = f.pm; r.ps = f.ps; r.pt = f.pt; r.ptz = f.ptz; r.pidx = f.pidx;
+  r.f_lse = fb; r.f_tl = fb + fbs; r.f_ce = fb + 2 * fbs; r.f_ent = fb + 3 * fbs;
+  r.f_cew = fb + 4 * fbs;
+  r.f_amax = fb_amax;
+  r.lse = a.lse; r.tlogit = a.target_logit; r.ce = a.ce; r.ent = a.entropy; r.cew_out = a.cew_out;
+  r.amax = reinterpret_cast<long long*>(a.argmax);
+  r.dx = need_grad ? a.dx : nullptr;
+  if (a.dtype == ESEP_DTYPE_F16)
+    head_step_rows_kernel<0><<<static_cast<unsigned>(m), 128, 0, s>>>(r);
+  else
+    head_step_rows_kernel<1><<<static_cast<unsigned>(m), 128, 0, s>>>(r);
+  if (cudaGetLastError() != cudaSuccess) return ESEP_ERR_CUDA;
+  head_step_scalars_kernel<<<1, 1024, 0, s>>>(m, a.v, a.ce, a.cew_out, a.entropy,
+                                              reinterpret_cast<const long long*>(a.argmax), tgt_o,
+                                              step_mode ? q.attn : nullptr, counts, status, a.loss,
+                                              a.metrics);
+  if (cudaGetLastError() != cudaSuccess) return ESEP_ERR_CUDA;
   return ESEP_OK;
 }
 }  // namespace
 
 extern "C" {
 
-size_t esep_head_train_workspace_bytes(int64_t n, int64_t h, int64_t v, int dtype) {
-  if (n <= 0 || h <= 0 || v <= 0 || h % 8 != 0) return 0;
+size_t esep_head_step_workspace_bytes(int64_t m, int64_t h, int64_t v, int dtype, int need_grad) {
+  if (m <= 0 || h <= 0 || v <= 0 || h % 8 != 0) return 0;
   if (dtype != ESEP_DTYPE_F16 && dtype != ESEP_DTYPE_BF16) return 0;
   const DeviceInfo* d = nullptr;
   if (current_device_info(&d) != ESEP_OK) return 0;
-  TrainLayout t;
-  if (train_layout(n, h, v, d, &t) != ESEP_OK) return 0;
+  StepLayout t;
+  if (step_layout(m, h, v, need_grad != 0, d, &t) != ESEP_OK) return 0;
   return t.total;
+}
+
+int esep_head_step(const void* x, int x_dtype, const void* w, const void* w_bf16, int dtype,
+                   int64_t m, int64_t h, int64_t v, const int64_t* target, const float* ce_weight,
+                   const int64_t* labels, const int64_t* attention_mask, int64_t seq_len,
+                   int need_grad, float* lse, float* target_logit, float* ce, float* entropy,
+                   int64_t* argmax, float* cew_out, float* loss, float* metrics, float* dx,
+                   int* overflow, void* workspace, size_t workspace_bytes, void* stream) {
+  StepArgs a = {};
+  a.x = x; a.x_dtype = x_dtype; a.w = w; a.w_bf16 = w_bf16; a.dtype = dtype;
+  a.m = m; a.h = h; a.v = v;
+  a.target = target; a.ce_weight = ce_weight; a.labels = labels;
+  a.attention_mask = attention_mask; a.seq_len = seq_len; a.need_grad = need_grad;
+  a.lse = lse; a.target_logit = target_logit; a.ce = ce; a.entropy = entropy; a.argmax = argmax;
+  a.cew_out = cew_out; a.loss = loss; a.metrics = metrics; a.dx = dx; a.overflow = overflow;
+  a.workspace = workspace; a.workspace_bytes = workspace_bytes; a.stream = stream;
+  return step_impl(a);
+}
+
+size_t esep_head_train_workspace_bytes(int64_t n, int64_t h, int64_t v, int dtype) {
+  return esep_head_step_workspace_bytes(n, h, v, dtype, 1);
 }
 
 int esep_head_train(const void* x, const void* w, const void* w_bf16, const int64_t* target,
@@ -763,139 +1185,28 @@ int esep_head_train(const void* x, const void* w, const void* w_bf16, const int6
                     float* target_logit, float* ce, float* entropy, int64_t* argmax,
                     float* cew_out, float* loss, float* metrics, float* dx, int* overflow,
                     void* workspace, size_t workspace_bytes, void* stream) {
-  int st = check_problem(x, w, n, h, v, dtype);
-  if (st != ESEP_OK) return st;
-  if (w_bf16 == nullptr || target == nullptr || ce_weight == nullptr || lse == nullptr ||
-      target_logit == nullptr || ce == nullptr || entropy == nullptr || argmax == nullptr ||
-      cew_out == nullptr || loss == nullptr || dx == nullptr || overflow == nullptr)
-    return ESEP_ERR_BAD_ARG;
-  if ((reinterpret_cast<uintptr_t>(dx) & 15u) || (reinterpret_cast<uintptr_t>(w_bf16) & 15u))
-    return ESEP_ERR_ALIGNMENT;
-  const DeviceInfo* d = nullptr;
-  st = current_device_info(&d);
-  if (st != ESEP_OK) return st;
-  TrainLayout t;
-  st = train_layout(n, h, v, d, &t);
-  if (st != ESEP_OK) return st;
-  if (workspace == nullptr || (reinterpret_cast<uintptr_t>(workspace) & (kAlign - 1)) ||
-      workspace_bytes < t.total)
-    return ESEP_ERR_WORKSPACE;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  uint8_t* ws = static_cast<uint8_t*>(workspace);
-  const esep_head_plan& pl = t.pl;
-
-  // 1. reference maximum per row: the forward sweep over a vocabulary prefix (record field 0)
-  float* record = reinterpret_cast<float*>(ws + t.record_off);
-  st = esep_head_forward_partial(x, w, target, n, h, std::min<int64_t>(v, kPrefixRows), 0, dtype,
-                                 record, workspace, t.base_bytes, stream);
-  if (st != ESEP_OK) return st;
-  if (cudaMemsetAsync(overflow, 0, sizeof(int), s) != cudaSuccess) return ESEP_ERR_CUDA;
-
-  // 2. the sweep
-  CUtensorMap tx, tw1, tw2;
-  if (make_tmap(&tx, x, dtype, n, h, bwd::BK, 64) != ESEP_OK) return ESEP_ERR_CUDA;
-  if (make_tmap(&tw1, w, dtype, v, h, bwd::BK, bwd::BV) != ESEP_OK) return ESEP_ERR_CUDA;
-  const bool w2_is_3d = (h % 64 == 0);
-  if (w2_is_3d) {
-    if (make_tmap_w3(&tw2, w_bf16, ESEP_DTYPE_BF16, v, h, bwd::G2_KV, 6) != ESEP_OK)
-      return ESEP_ERR_CUDA;
-  } else if (make_tmap(&tw2, w_bf16, ESEP_DTYPE_BF16, v, h, 64, bwd::G2_KV) != ESEP_OK) {
-    return ESEP_ERR_CUDA;
+  if (target == nullptr || ce_weight == nullptr || overflow == nullptr) return ESEP_ERR_BAD_ARG;
+  // the four scalars of the older interface are the first four of the step's eight
+  float* m8 = nullptr;
+  if (metrics != nullptr) {
+    if (workspace == nullptr || workspace_bytes < kAlign) return ESEP_ERR_WORKSPACE;
+    m8 = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + 128);   // status block
   }
-  const size_t st_stride = align_up(t.st_elems * sizeof(float));
-  const size_t lo_stride = align_up(t.lo_elems * sizeof(float));
-  TrainParams p;
-  p.n = static_cast<int>(n);
-  p.h = static_cast<int>(h);
-  p.v = static_cast<int>(v);
-  p.n_row_tiles = pl.fwd_row_tiles;
-  p.nhb = pl.bwd_hblocks;
-  p.total_steps = pl.bwd_total_steps;
-  p.full_rounds = pl.bwd_full_rounds;
-  p.rem_tp = pl.bwd_rem_pairs;
-  p.rem_splits = pl.bwd_rem_splits;
-  p.steps_per_split = pl.bwd_steps_per_split;
-  p.m_ref = record;
-  p.target = reinterpret_cast<const long long*>(target);
-  p.dx = dx;
-  p.dx_part = reinterpret_cast<float*>(ws + pl.ws_dxpart_off);
-  p.st_s = reinterpret_cast<float*>(ws + t.st_off);
-  p.st_t = reinterpret_cast<float*>(ws + t.st_off + st_stride);
-  p.st_key = reinterpret_cast<int*>(ws + t.st_off + 2 * st_stride);
-  p.st_idx = reinterpret_cast<int*>(ws + t.st_off + 3 * st_stride);
-  p.lo_s = reinterpret_cast<float*>(ws + t.lo_off);
-  p.lo_t = reinterpret_cast<float*>(ws + t.lo_off + lo_stride);
-  p.lo_key = reinterpret_cast<int*>(ws + t.lo_off + 2 * lo_stride);
-  p.lo_idx = reinterpret_cast<int*>(ws + t.lo_off + 3 * lo_stride);
-  p.w2_is_3d = w2_is_3d ? 1 : 0;
-  p.overflow = overflow;
-  p.status = reinterpret_cast<int*>(ws + pl.ws_status_off);
+  const int st = esep_head_step(x, dtype, w, w_bf16, dtype, n, h, v, target, ce_weight, nullptr,
+                                nullptr, 0, 1, lse, target_logit, ce, entropy, argmax, cew_out, loss,
+                                m8, dx, overflow, workspace, workspace_bytes, stream);
+  if (st != ESEP_OK || metrics == nullptr) return st;
+  return cudaMemcpyAsync(metrics, m8, ESEP_METRIC_SCALARS * sizeof(float),
+                         cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream)) == cudaSuccess
+             ? ESEP_OK
+             : ESEP_ERR_CUDA;
+}
 
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(static_cast<unsigned>(pl.bwd_grid));
-  cfg.blockDim = dim3(trn::THREADS_T);
-  cfg.dynamicSmemBytes = trn::SMEM_BYTES_T;
-  cfg.stream = s;
-  cudaLaunchAttribute attr;
-  attr.id = cudaLaunchAttributeClusterDimension;
-  attr.val.clusterDim.x = kBwdCluster;
-  attr.val.clusterDim.y = 1;
-  attr.val.clusterDim.z = 1;
-  cfg.attrs = &attr;
-  cfg.numAttrs = 1;
-  cudaError_t e;
-  if (dtype == ESEP_DTYPE_F16)
-    e = cudaLaunchKernelEx(&cfg, head_train_kernel<0>, tx, tw1, tw2, p);
-  else
-    e = cudaLaunchKernelEx(&cfg, head_train_kernel<1>, tx, tw1, tw2, p);
-  if (e != cudaSuccess) {
-    cudaGetLastError();
-    return ESEP_ERR_CUDA;
-  }
-
-  // 3. per-row finish (statistics, dHidden in place) and the scalars
-  TrainRowsParams q;
-  q.n = p.n;
-  q.h = p.h;
-  q.v = p.v;
-  q.n_row_tiles = pl.fwd_row_tiles;
-  q.n_clusters = pl.bwd_grid / kBwdCluster;
-  q.full_rounds = pl.bwd_full_rounds;
-  q.rem_tp = pl.bwd_rem_pairs;
-  q.rem_splits = pl.bwd_rem_splits;
-  q.pass_w = kBwdCluster * pl.bwd_hslice;
-  q.x = x;
-  q.w = w;
-  q.target = reinterpret_cast<const long long*>(target);
-  q.ce_weight = ce_weight;
-  q.m_ref = record;
-  q.st_s = p.st_s; q.st_t = p.st_t; q.lo_s = p.lo_s; q.lo_t = p.lo_t;
-  q.st_key = p.st_key; q.st_idx = p.st_idx; q.lo_key = p.lo_key; q.lo_idx = p.lo_idx;
-  q.dx_part = p.dx_part;
-  q.dx = dx;
-  q.lse = lse; q.tlogit = target_logit; q.ce = ce; q.ent = entropy; q.cew_out = cew_out;
-  q.amax = reinterpret_cast<long long*>(argmax);
-  if (dtype == ESEP_DTYPE_F16)
-    head_train_rows_kernel<0><<<static_cast<unsigned>(n), 128, 0, s>>>(q);
-  else
-    head_train_rows_kernel<1><<<static_cast<unsigned>(n), 128, 0, s>>>(q);
-  if (cudaGetLastError() != cudaSuccess) return ESEP_ERR_CUDA;
-  head_scalars_kernel<<<1, 1024, 0, s>>>(p.n, v, ce, cew_out, entropy,
-                                         reinterpret_cast<const long long*>(argmax),
-                                         reinterpret_cast<const long long*>(target), p.status, loss,
-                                         metrics);
-  if (cudaGetLastError() != cudaSuccess) return ESEP_ERR_CUDA;
-
-  // 4. guarded second attempt: the two-kernel path, enqueued behind the flag. Its kernels return
-  //    at once unless a row overflowed; if one did they overwrite every output of this call.
-  g_gate = overflow;
-  st = esep_head_forward(x, w, target, ce_weight, n, h, v, dtype, lse, target_logit, ce, entropy,
-                         argmax, cew_out, loss, metrics, workspace, t.base_bytes, stream);
-  if (st == ESEP_OK)
-    st = esep_head_backward(x, w, target, cew_out, lse, n, h, v, 0, dtype, dx, workspace,
-                            t.base_bytes, stream);
-  g_gate = nullptr;
-  return st;
+int esep_head_debug_counters(long long* out, int n) {
+  if (out == nullptr || n < 2) return ESEP_ERR_BAD_ARG;
+  out[0] = g_init_calls.load();
+  out[1] = g_tmap_encodes.load();
+  return ESEP_OK;
 }
 
 }  // extern "C"

@@ -97,6 +97,32 @@ static constexpr int SMEM_BYTES =
 static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KiB of shared memory a CTA may use");
 }  // namespace bwd
 
+// Work split of the clustered sweeps. `n_tp` (row tile, pass) pairs go to `ncl` clusters:
+//  1. full rounds: in round r cluster k sweeps pair r * ncl + k through the whole vocabulary;
+//  2. the rem_tp < ncl left-over pairs are each cut into rem_splits vocabulary runs of
+//     steps_per_split steps, so that (almost) every cluster gets one run.
+// Pure integer arithmetic shared by the host plan and by kernels that learn their row count on
+// the device.
+struct SweepSplit {
+  int full_rounds, rem_tp, rem_splits, steps_per_split;
+};
+__host__ __device__ inline SweepSplit sweep_split(long long n_tp, int ncl, int total_steps) {
+  SweepSplit r;
+  if (ncl < 1) ncl = 1;
+  r.full_rounds = static_cast<int>(n_tp / ncl);
+  r.rem_tp = static_cast<int>(n_tp - static_cast<long long>(r.full_rounds) * ncl);
+  r.rem_splits = 0;
+  r.steps_per_split = 0;
+  if (r.rem_tp > 0 && total_steps > 0) {
+    int want = ncl / r.rem_tp;
+    if (want > total_steps) want = total_steps;
+    if (want < 1) want = 1;
+    r.steps_per_split = (total_steps + want - 1) / want;
+    r.rem_splits = (total_steps + r.steps_per_split - 1) / r.steps_per_split;
+  }
+  return r;
+}
+
 template <int kFmt>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   if (kFmt == 0) {

@@ -56,7 +56,53 @@ struct FwdParams {
   int* pidx;           // [n_splits, n] local index of the partial max
   int* status;         // device status word
   const int* gate;     // null, or a device flag: the kernel does nothing when it reads 0
+  // Rows known only on the device: when `row_range` is set the kernel sweeps the rows
+  // [row_range[0], row_range[1]) of x (both read on the device, end <= n) and derives its own
+  // work split from their number (fwd_split_rows); partial records then sit at
+  // [split][row - row_range[0]] with a stride of fwd_split_rows().stride.
+  const int* row_range;
+  int part_cap;        // rows the partial arrays hold (splits * stride never exceeds it)
 };
+
+// Work split of the forward sweep for a row count that is only known on the device: the
+// vocabulary tiles of every row pair are cut into `splits` runs of `tiles_per_unit` tiles so
+// that the units fill the resident CTA pairs evenly (the first split count that reaches 97 %,
+// else the best), subject to splits * stride <= part_cap. Cheap enough for every thread.
+struct FwdSplit {
+  int n_row_tiles, n_row_pairs, tiles_per_unit, n_splits, stride;
+};
+__host__ __device__ inline FwdSplit fwd_split_rows(int n_rows, int n_vtiles, int n_pairs,
+                                                   int part_cap) {
+  FwdSplit r;
+  r.n_row_tiles = (n_rows + 127) / 128;
+  r.n_row_pairs = (r.n_row_tiles + 1) / 2;
+  r.stride = r.n_row_pairs * 256;
+  r.tiles_per_unit = n_vtiles > 0 ? n_vtiles : 1;
+  r.n_splits = 1;
+  if (r.n_row_pairs <= 0 || n_vtiles <= 0) {
+    r.n_splits = 0;
+    return r;
+  }
+  if (n_pairs < 1) n_pairs = 1;
+  int max_splits = r.stride > 0 ? part_cap / r.stride : 1;
+  if (max_splits > 128) max_splits = 128;
+  if (max_splits > n_vtiles) max_splits = n_vtiles;
+  const float ideal = static_cast<float>(r.n_row_pairs) * n_vtiles / n_pairs;
+  float best = -1.f;
+  for (int want = 1; want <= max_splits; ++want) {
+    const int tpu = (n_vtiles + want - 1) / want;
+    const int splits = (n_vtiles + tpu - 1) / tpu;
+    const int waves = (r.n_row_pairs * splits + n_pairs - 1) / n_pairs;
+    const float eff = ideal / (static_cast<float>(waves) * tpu);
+    if (eff > best + 1e-6f) {
+      best = eff;
+      r.tiles_per_unit = tpu;
+      r.n_splits = splits;
+    }
+    if (eff >= 0.97f) break;
+  }
+  return r;
+}
 
 namespace fwd {
 static constexpr int BM = 128;      // rows per tile (TMEM lanes)
@@ -152,11 +198,23 @@ head_fwd_kernel(const __grid_constant__ CUtensorMap tmap_x,
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int kblocks = (p.h + BK - 1) / BK;
-  const int n_units = p.n_row_pairs * p.n_splits;
   const uint32_t c = cluster_ctarank();   // 0 = pair leader, 1 = peer
   const bool is_leader = (c == 0);
   const int pair_id = blockIdx.x >> 1;
   const int n_pairs = gridDim.x >> 1;
+  // Rows and work split: from the host plan, or from the device row range.
+  int row0 = 0, row_end = p.n, n_row_pairs = p.n_row_pairs, tiles_per_unit = p.tiles_per_unit;
+  int n_splits = p.n_splits, pstride = p.n;
+  if (p.row_range != nullptr) {
+    row0 = p.row_range[0];
+    row_end = min(p.row_range[1], p.n);
+    const FwdSplit fs = fwd_split_rows(max(row_end - row0, 0), p.n_vtiles, n_pairs, p.part_cap);
+    n_row_pairs = fs.n_row_pairs;
+    tiles_per_unit = fs.tiles_per_unit;
+    n_splits = fs.n_splits;
+    pstride = fs.stride;
+  }
+  const int n_units = n_row_pairs * n_splits;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -191,10 +249,10 @@ head_fwd_kernel(const __grid_constant__ CUtensorMap tmap_x,
     bool ok = true;
     const uint32_t full_leader0 = mapa_shared(full_bar(0), 0);
     for (int u = pair_id; u < n_units && ok; u += n_pairs) {
-      const int rt = 2 * (u % p.n_row_pairs) + static_cast<int>(c);
-      const int sp = u / p.n_row_pairs;
-      const int vt0 = sp * p.tiles_per_unit;
-      const int vt1 = min(vt0 + p.tiles_per_unit, p.n_vtiles);
+      const int rt = 2 * (u % n_row_pairs) + static_cast<int>(c);
+      const int sp = u / n_row_pairs;
+      const int vt0 = sp * tiles_per_unit;
+      const int vt1 = min(vt0 + tiles_per_unit, p.n_vtiles);
       for (int vt = vt0; vt < vt1 && ok; ++vt) {
         for (int kb = 0; kb < kblocks; ++kb) {
           ok = mbar_wait_warp<true>(empty_bar(stage), phase ^ 1u, abort_flag);
@@ -204,7 +262,7 @@ head_fwd_kernel(const __grid_constant__ CUtensorMap tmap_x,
             // the leader's barrier counts the bytes of both CTAs
             if (is_leader) mbar_expect_tx(full_bar(stage), 2 * STAGE_BYTES);
             const uint32_t bar = full_leader0 + 8u * stage;
-            tma_load_2d_pair(sa, &tmap_x, bar, kb * BK, rt * BM);
+            tma_load_2d_pair(sa, &tmap_x, bar, kb * BK, row0 + rt * BM);
             tma_load_2d_pair(sa + A_BYTES, &tmap_w, bar, kb * BK,
                              vt * BN + static_cast<int>(c) * (BN / 2));
           }
@@ -228,9 +286,9 @@ head_fwd_kernel(const __grid_constant__ CUtensorMap tmap_x,
       uint32_t stage = 0, phase = 0, acc = 0, aphase = 0;
       bool ok = true;
       for (int u = pair_id; u < n_units && ok; u += n_pairs) {
-        const int sp = u / p.n_row_pairs;
-        const int vt0 = sp * p.tiles_per_unit;
-        const int vt1 = min(vt0 + p.tiles_per_unit, p.n_vtiles);
+        const int sp = u / n_row_pairs;
+        const int vt0 = sp * tiles_per_unit;
+        const int vt1 = min(vt0 + tiles_per_unit, p.n_vtiles);
         for (int vt = vt0; vt < vt1 && ok; ++vt) {
           // both CTAs' epilogues must have drained this accumulator
           ok = mbar_wait_warp<true>(tempty_bar(acc), aphase ^ 1u, abort_flag);
@@ -275,13 +333,13 @@ head_fwd_kernel(const __grid_constant__ CUtensorMap tmap_x,
     bool ok = true;
     const uint32_t tempty_leader0 = mapa_shared(tempty_bar(0), 0);
     for (int u = pair_id; u < n_units && ok; u += n_pairs) {
-      const int rt = 2 * (u % p.n_row_pairs) + static_cast<int>(c);
-      const int sp = u / p.n_row_pairs;
-      const int vt0 = sp * p.tiles_per_unit;
-      const int vt1 = min(vt0 + p.tiles_per_unit, p.n_vtiles);
-      const int row = rt * BM + row_in_tile;
+      const int rt = 2 * (u % n_row_pairs) + static_cast<int>(c);
+      const int sp = u / n_row_pairs;
+      const int vt0 = sp * tiles_per_unit;
+      const int vt1 = min(vt0 + tiles_per_unit, p.n_vtiles);
+      const int row = row0 + rt * BM + row_in_tile;
       int tgt_local = -1;
-      if (row < p.n) {
+      if (row < row_end) {
         const long long tg = p.target[row] - p.vocab_offset;
         if (tg >= 0 && tg < p.v) tgt_local = static_cast<int>(tg);
       }
@@ -314,8 +372,8 @@ head_fwd_kernel(const __grid_constant__ CUtensorMap tmap_x,
         acc ^= 1u;
         aphase ^= acc ^ 1u;  // flips when acc wraps back to 0
       }
-      if (ok && row < p.n) {
-        const size_t o = static_cast<size_t>(sp) * p.n + row;
+      if (ok && row < row_end) {
+        const size_t o = static_cast<size_t>(sp) * pstride + (row - row0);
         p.pm[o] = st.m;
         p.ps[o] = st.s;
         p.pt[o] = st.t2 * LN2;

@@ -27,9 +27,10 @@
 //     extra per-row reductions fit the register file: per 32-row chunk a butterfly over the warp
 //     turns "each lane holds 32 rows of its own vocabulary row" into "each lane holds one row
 //     summed over the warp's 32 vocabulary rows" in 31 shuffles; the row maximum comes from the
-//     same butterfly with an integer max on a key (the float's order-preserving integer with the
-//     low 5 bits replaced by 31 - lane, so equal logits resolve to the lowest vocabulary index
-//     and the index needs no second pass). P is packed and handed to G2 first, the sums follow;
+//     same butterfly with fmaxf on the exact fp32 logits, and only when some row of the chunk
+//     beats its running maximum (strictly: an earlier, i.e. lower, vocabulary index keeps equal
+//     values) a second pass finds the lowest lane that holds that maximum (kernels.py:60, 75:
+//     first index of the max). P is packed and handed to G2 first, the sums follow;
 //   * the accumulator is drained raw; the -onehot term and all scaling moved to the row kernel;
 //   * the row's TARGET entry is left out of P and of the sums: for a confident row p_target / s is
 //     1 - tiny, and forming it from a bf16-rounded p would lose the tiny part. The row kernel adds
@@ -48,14 +49,11 @@ enum : int {
 };
 
 struct TrainParams {
-  int n, h, v;
-  int n_row_tiles;        // ceil(n / 128)
+  int n, h, v;            // n: rows the arrays below are laid out for (and swept, unless n_dev)
+  const int* n_dev;       // null, or device word: only rows [0, *n_dev) are swept (*n_dev <= n);
+                          // the work split is then derived on the device (sweep_split)
   int nhb;                // 128-wide H blocks per CTA (1..3)
   int total_steps;        // ceil(ceil(v / 128) / 4)
-  int full_rounds;        // rounds in which every cluster sweeps one whole (row tile, pass)
-  int rem_tp;             // (row tile, pass) pairs left over after the full rounds
-  int rem_splits;         // vocabulary runs each left-over pair is cut into (0 if none)
-  int steps_per_split;    // steps per such run
   const float* m_ref;     // [n] row maximum over the vocabulary prefix (REF_MARGIN is added here)
   const long long* target;  // [n] target ids; a valid target's entry is excluded from P and the sums
   float* dx;              // [n, h] raw accumulator of the directly written tiles
@@ -64,11 +62,11 @@ struct TrainParams {
   // pass 0 only. Direct tiles: st_*[slot][row]; left-over tiles: lo_*[run * 16 + slot][j * 128 + r].
   float* st_s;
   float* st_t;
-  int* st_key;            // ordered key of the largest logit (see float_key), -2^31 if none
-  int* st_idx;            // its local vocabulary index
+  float* st_max;          // largest logit of the slot's vocabulary rows (-inf if none), exact
+  int* st_idx;            // its vocabulary index: the lowest one among equal logits
   float* lo_s;
   float* lo_t;
-  int* lo_key;
+  float* lo_max;
   int* lo_idx;
   int w2_is_3d;
   int* overflow;          // set to 1 when a row's maximum is more than OVERFLOW_NATS above m_ref
@@ -78,23 +76,18 @@ struct TrainParams {
 namespace trn {
 using namespace bwd;
 static constexpr int EPI_WARPS = 8;
+static constexpr int KC_PER_BLOCK = BV / G2_KV;   // G2 K-chunks per 128-row vocabulary block
 static constexpr int THREADS_T = 128 + EPI_WARPS * 32;   // 384
 static constexpr float REF_MARGIN = 40.f;      // added to the prefix maximum: the reference m_ref
 static constexpr float OVERFLOW_NATS = 75.f;   // largest z - m_ref the sweep accepts
 static constexpr int ROWDATA_T = 2 * BM * 4;             // c2[128], local target id [128]
+// barriers: full[6] empty[6] s_full s_empty p_empty dx_full dx_empty rd_ready rd_free stage_ready
+//           p_in[4] p_peer[4]
+static constexpr int NUM_BARS_T = 2 * SLOTS + 8 + 2 * CL;
 static constexpr int SMEM_BYTES_T =
-    1024 + P_BYTES + STAGE_BYTES + SLOTS * SLOT_BYTES + NUM_BARS * 8 + 64 + 16 + ROWDATA_T;
+    1024 + P_BYTES + STAGE_BYTES + SLOTS * SLOT_BYTES + NUM_BARS_T * 8 + 64 + 16 + ROWDATA_T;
 static_assert(SMEM_BYTES_T <= 232448, "exceeds the 227 KiB of shared memory a CTA may use");
 }  // namespace trn
-
-// Monotone map from float order to signed-integer order.
-__device__ __forceinline__ int float_key(float z) {
-  const int b = __float_as_int(z);
-  return b ^ ((b >> 31) & 0x7fffffff);
-}
-__device__ __forceinline__ float key_float(int k) {
-  return __int_as_float(k ^ ((k >> 31) & 0x7fffffff));
-}
 
 // v[j] (j = 0..31) of every lane -> returns, in lane l, the sum over all lanes of their v[l].
 // 31 shuffles; v is destroyed.
@@ -132,15 +125,18 @@ head_train_kernel(const __grid_constant__ CUtensorMap tmap_x,    // x [n, h], bo
   auto ring_empty = [&](int s) { return bars + 8u * (SLOTS + s); };
   const uint32_t s_full = bars + 8u * (2 * SLOTS + 0);
   const uint32_t s_empty = bars + 8u * (2 * SLOTS + 1);
-  const uint32_t p_in = bars + 8u * (2 * SLOTS + 2);
-  const uint32_t p_peer = bars + 8u * (2 * SLOTS + 3);
-  const uint32_t p_empty = bars + 8u * (2 * SLOTS + 4);
-  const uint32_t dx_full = bars + 8u * (2 * SLOTS + 5);
-  const uint32_t dx_empty = bars + 8u * (2 * SLOTS + 6);
-  const uint32_t rd_ready = bars + 8u * (2 * SLOTS + 7);
-  const uint32_t rd_free = bars + 8u * (2 * SLOTS + 8);
-  const uint32_t stage_ready = bars + 8u * (2 * SLOTS + 9);
-  const int misc_off = P_BYTES + STAGE_BYTES + SLOTS * SLOT_BYTES + NUM_BARS * 8;
+  const uint32_t p_empty = bars + 8u * (2 * SLOTS + 2);
+  const uint32_t dx_full = bars + 8u * (2 * SLOTS + 3);
+  const uint32_t dx_empty = bars + 8u * (2 * SLOTS + 4);
+  const uint32_t rd_ready = bars + 8u * (2 * SLOTS + 5);
+  const uint32_t rd_free = bars + 8u * (2 * SLOTS + 6);
+  const uint32_t stage_ready = bars + 8u * (2 * SLOTS + 7);
+  // One barrier per 128-row vocabulary block of the P buffer (block b is produced by CTA b):
+  // p_in(b): block b of this CTA's buffer holds the current step; p_peer(b) (leader only): the
+  // pair peer's buffer does too.
+  auto p_in = [&](uint32_t b) { return bars + 8u * (2 * SLOTS + 8 + b); };
+  auto p_peer = [&](uint32_t b) { return bars + 8u * (2 * SLOTS + 8 + CL + b); };
+  const int misc_off = P_BYTES + STAGE_BYTES + SLOTS * SLOT_BYTES + NUM_BARS_T * 8;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen_base + misc_off);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + misc_off + 8);
   float* row_c2 = reinterpret_cast<float*>(gen_base + ((misc_off + 64 + 15) & ~15));  // float4 reads
@@ -158,11 +154,16 @@ head_train_kernel(const __grid_constant__ CUtensorMap tmap_x,    // x [n, h], bo
   // Work decomposition: the one of head_bwd_kernel (full rounds in lock step, then one
   // vocabulary run per cluster for the left-over tiles).
   const int n_clusters = gridDim.x / CL;
-  const long long full_len = static_cast<long long>(p.full_rounds) * p.total_steps;
-  const bool has_rem = cluster_id < p.rem_tp * p.rem_splits;
+  const int hs = p.nhb * 128;
+  const int n_rows = p.n_dev != nullptr ? min(*p.n_dev, p.n) : p.n;   // rows swept by this launch
+  const int n_row_tiles = (n_rows + BM - 1) / BM;
+  const int n_passes = (p.h + CL * hs - 1) / (CL * hs);
+  const SweepSplit split =
+      sweep_split(static_cast<long long>(n_row_tiles) * n_passes, n_clusters, p.total_steps);
+  const long long full_len = static_cast<long long>(split.full_rounds) * p.total_steps;
+  const bool has_rem = cluster_id < split.rem_tp * split.rem_splits;
   const long long u_first = (full_len > 0 || has_rem) ? 0 : 1;
   const long long u_last = full_len + (has_rem ? 1 : 0);
-  const int hs = p.nhb * 128;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < SLOTS; ++s) {
@@ -171,11 +172,14 @@ head_train_kernel(const __grid_constant__ CUtensorMap tmap_x,    // x [n, h], bo
     }
     mbar_init(s_full, 1);                   // pair commit
     mbar_init(s_empty, 2 * EPI_WARPS);      // epilogue warps of both CTAs (leader's barrier)
-    mbar_init(p_in, 1 + EPI_WARPS / 2);     // arming arrive + the warps that write the own half
-    mbar_init(p_peer, 1);
+    for (uint32_t b = 0; b < CL; ++b) {
+      // own block: the epilogue warps that write it; other blocks: the arming arrive (+ 16 KiB)
+      mbar_init(p_in(b), b == c ? EPI_WARPS / 2 : 1);
+      mbar_init(p_peer(b), 1);              // relay arrive from the pair peer
+    }
     mbar_init(rd_free, EPI_WARPS);
     mbar_init(stage_ready, EPI_WARPS);      // every line of this step's P block is in place
-    mbar_init(p_empty, 2);                  // one commit per pair
+    mbar_init(p_empty, 2);                  // one commit per pair, after THIS CTA's block is consumed
     mbar_init(dx_full, 1);
     mbar_init(dx_empty, 2 * EPI_WARPS);
     mbar_init(rd_ready, EPI_WARPS * 32);
@@ -199,17 +203,17 @@ head_train_kernel(const __grid_constant__ CUtensorMap tmap_x,    // x [n, h], bo
 
   auto unit_tp = [&](long long u) {
     return u < full_len ? static_cast<int>(u / p.total_steps) * n_clusters + cluster_id
-                        : p.full_rounds * n_clusters + cluster_id % p.rem_tp;
+                        : split.full_rounds * n_clusters + cluster_id % split.rem_tp;
   };
-  auto unit_rt = [&](long long u) { return unit_tp(u) % p.n_row_tiles; };
-  auto unit_pass = [&](long long u) { return unit_tp(u) / p.n_row_tiles; };
+  auto unit_rt = [&](long long u) { return unit_tp(u) % n_row_tiles; };
+  auto unit_pass = [&](long long u) { return unit_tp(u) / n_row_tiles; };
   auto unit_steps = [&](long long u, int& s0, int& s1) {
     if (u < full_len) {
       s0 = 0;
       s1 = p.total_steps;
     } else {
-      s0 = (cluster_id / p.rem_tp) * p.steps_per_split;
-      s1 = min(p.total_steps, s0 + p.steps_per_split);
+      s0 = (cluster_id / split.rem_tp) * split.steps_per_split;
+      s1 = min(p.total_steps, s0 + split.steps_per_split);
     }
   };
   auto unit_next = [&](long long u) { return u < full_len ? u + p.total_steps : u + 1; };
@@ -336,24 +340,33 @@ head_train_kernel(const __grid_constant__ CUtensorMap tmap_x,    // x [n, h], bo
       constexpr uint32_t idesc2 = make_idesc(1, 256, BM, 1, 1);  // bf16, MN-major A and B
       uint32_t stage = 0, phase = 0, g2par = 0, upar = 0;
       bool ok = true;
+      if (elected)   // first step: 16 KiB from each of the three other CTAs
+        for (uint32_t b = 0; b < CL; ++b)
+          if (b != c) mbar_expect_tx(p_in(b), HALF_BYTES);
       for (long long u = u_first; u < u_last && ok; u = unit_next(u)) {
         int s0, s1;
         unit_steps(u, s0, s1);
         for (int step = s0; step < s1 && ok; ++step) {
-          if (elected) mbar_expect_tx(p_in, 3 * HALF_BYTES);
-          ok = mbar_wait_warp<true>(p_in, g2par, abort_flag) &&
-               mbar_wait_warp<true>(p_peer, g2par, abort_flag);
-          if (!ok) break;
-          fence_proxy_async();
-          tc_fence_after();
-          if (step == s0) {
-            ok = mbar_wait_warp<true>(dx_empty, upar ^ 1u, abort_flag);
-            if (!ok) break;
-            tc_fence_after();
-          }
           uint64_t bdesc = make_smem_desc(p_base, 8192, 1024);
           uint32_t acc0 = (step == s0) ? 0u : 1u;
           for (int kc = 0; kc < STEP_V / G2_KV; ++kc) {
+            if ((kc & (KC_PER_BLOCK - 1)) == 0) {
+              // block b of P (from CTA b) must be in this CTA's buffer and in the peer's
+              const uint32_t b = static_cast<uint32_t>(kc / KC_PER_BLOCK);
+              ok = mbar_wait_warp<true>(p_in(b), g2par, abort_flag) &&
+                   mbar_wait_warp<true>(p_peer(b), g2par, abort_flag);
+              if (!ok) break;
+              // arm the block's barrier for the next step: its data can only be sent after this
+              // step's MMAs on the block have retired (p_empty), so the arming always comes first
+              if (elected && b != c) mbar_expect_tx(p_in(b), HALF_BYTES);
+              fence_proxy_async();
+              tc_fence_after();
+              if (step == s0 && kc == 0) {
+                ok = mbar_wait_warp<true>(dx_empty, upar ^ 1u, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+              }
+            }
             ok = mbar_wait_warp<true>(ring_full(SLOTS_A + stage), phase, abort_flag);
             if (!ok) break;
             tc_fence_after();
@@ -366,6 +379,10 @@ head_train_kernel(const __grid_constant__ CUtensorMap tmap_x,    // x [n, h], bo
                 umma_f16_ss_pair(d, adesc + 512u * hb + 128u, bdesc + 128u, idesc2, 1u);
               }
               umma_commit_pair_mask(ring_empty(SLOTS_A + stage), pair_mask);
+              // block kc / 4 of every P buffer this pair reads is free once these MMAs retire:
+              // tell the CTA that produces it (the other pair's commit completes its barrier)
+              if ((kc & (KC_PER_BLOCK - 1)) == KC_PER_BLOCK - 1)
+                umma_commit_pair_mask(p_empty, static_cast<uint16_t>(1u << (kc / KC_PER_BLOCK)));
             }
             acc0 = 1u;
             bdesc += 256u;
@@ -374,7 +391,6 @@ head_train_kernel(const __grid_constant__ CUtensorMap tmap_x,    // x [n, h], bo
               phase ^= 1u;
             }
           }
-          if (ok && elected) umma_commit_pair_mask(p_empty, static_cast<uint16_t>(0xF));
           g2par ^= 1u;
         }
         if (ok && elected) umma_commit_pair_mask(dx_full, pair_mask);
@@ -387,17 +403,24 @@ head_train_kernel(const __grid_constant__ CUtensorMap tmap_x,    // x [n, h], bo
     } else {
       // Pair peer: arms the local P barrier each step and relays its completion to the leader.
       const bool elected = elect_one_sync();
-      const uint32_t p_peer_leader = mapa_shared(p_peer, leader);
+      const uint32_t p_peer_leader0 = mapa_shared(p_peer(0), leader);
       uint32_t par = 0;
       bool ok = true;
+      if (elected)
+        for (uint32_t b = 0; b < CL; ++b)
+          if (b != c) mbar_expect_tx(p_in(b), HALF_BYTES);
       for (long long u = u_first; u < u_last && ok; u = unit_next(u)) {
         int s0, s1;
         unit_steps(u, s0, s1);
-        for (int s = s0; s < s1; ++s) {
-          if (elected) mbar_expect_tx(p_in, 3 * HALF_BYTES);
-          ok = mbar_wait_warp<true>(p_in, par, abort_flag);
-          if (!ok) break;
-          if (elected) mbar_arrive_remote(p_peer_leader);
+        for (int s = s0; s < s1 && ok; ++s) {
+          for (uint32_t b = 0; b < CL; ++b) {
+            ok = mbar_wait_warp<true>(p_in(b), par, abort_flag);
+            if (!ok) break;
+            if (elected) {
+              mbar_arrive_remote(p_peer_leader0 + 8u * b);
+              if (b != c) mbar_expect_tx(p_in(b), HALF_BYTES);   // next step (see the leader)
+            }
+          }
           par ^= 1u;
         }
       }
@@ -426,8 +449,6 @@ head_train_kernel(const __grid_constant__ CUtensorMap tmap_x,    // x [n, h], bo
     const uint32_t p_xor = static_cast<uint32_t>(vi & 7);
     const bool copy_warp = (warp == 4);
     const bool copy_lane = copy_warp && elect_one_sync();
-    const int lane_low = 31 - lane;
-    constexpr int KEY_NONE = static_cast<int>(0x80000000u);
     for (long long u = u_first; u < u_last && ok; u = unit_next(u)) {
       const int rt = unit_rt(u);
       const bool direct = (u < full_len);
@@ -442,7 +463,7 @@ head_train_kernel(const __grid_constant__ CUtensorMap tmap_x,    // x [n, h], bo
         const int row = rt * BM + et;
         float c2 = NEG_BIG;
         int tg = -1;
-        if (row < p.n) {
+        if (row < n_rows) {
           c2 = -(p.m_ref[row] + REF_MARGIN) * LOG2E;
           const long long t = p.target[row];
           if (t >= 0 && t < p.v) tg = static_cast<int>(t);
@@ -456,7 +477,8 @@ head_train_kernel(const __grid_constant__ CUtensorMap tmap_x,    // x [n, h], bo
       // Running statistics: lane l owns rows hf*64 + ch*32 + l (ch = 0, 1) of the tile, summed
       // over the 32 vocabulary rows of this warp and over the steps of the unit.
       float s_run[2] = {0.f, 0.f}, t_run[2] = {0.f, 0.f};
-      int k_run[2] = {KEY_NONE, KEY_NONE}, i_run[2] = {0, 0};
+      float m_run[2] = {-INFINITY, -INFINITY};
+      int i_run[2] = {0, 0};
       uint32_t z0[32], z1[32];   // raw logits of the next step (two 32-row chunks)
       uint32_t pk[32];           // packed bf16 P of the current step (64 rows)
       auto drain_logits = [&]() {
@@ -501,28 +523,38 @@ head_train_kernel(const __grid_constant__ CUtensorMap tmap_x,    // x [n, h], bo
         const int* tgp = row_tg + hf * 64 + ch * 32;
         const int my_v = vbase + lane;
         float tmp[32];
-        // largest logit per row over this warp's 32 vocabulary rows (integer keys)
+        // Largest logit per row over this warp's 32 vocabulary rows: the butterfly leaves, in lane
+        // l, the exact maximum of row l. Which vocabulary row holds it is looked up only when a
+        // row beats its running maximum (rare once the sweep is under way).
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int key = (float_key(__uint_as_float(z[j])) & ~31) | lane_low;
-          tmp[j] = __int_as_float(v_ok ? key : KEY_NONE);
-        }
+        for (int j = 0; j < 32; ++j) tmp[j] = v_ok ? __uint_as_float(z[j]) : -INFINITY;
 #pragma unroll
         for (int w = 16; w >= 1; w >>= 1) {
           const bool up = (lane & w) != 0;
 #pragma unroll
           for (int k = 0; k < w; ++k) {
-            const int send = __float_as_int(up ? tmp[k] : tmp[k + w]);
-            const int keep = __float_as_int(up ? tmp[k + w] : tmp[k]);
-            tmp[k] = __int_as_float(max(keep, __shfl_xor_sync(0xffffffffu, send, w)));
+            const float send = up ? tmp[k] : tmp[k + w];
+            const float keep = up ? tmp[k + w] : tmp[k];
+            tmp[k] = fmaxf(keep, __shfl_xor_sync(0xffffffffu, send, w));
           }
         }
         {
-          const int km = __float_as_int(tmp[0]);
-          // stored keys carry low bits 31, so only a strictly larger logit replaces an earlier one
-          if (km > k_run[ch]) {
-            k_run[ch] = km | 31;
-            i_run[ch] = vbase + 31 - (km & 31);
+          const float cm = tmp[0];
+          // strict: an equal value met earlier sits at a lower vocabulary index and stays
+          const bool better = cm > m_run[ch];
+          if (__any_sync(0xffffffffu, better)) {
+            int first = 0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float mj = __shfl_sync(0xffffffffu, cm, j);
+              const unsigned hit =
+                  __ballot_sync(0xffffffffu, v_ok && __uint_as_float(z[j]) == mj);
+              if (lane == j) first = __ffs(hit) - 1;   // lowest lane = lowest vocabulary row
+            }
+            if (better) {
+              m_run[ch] = cm;
+              i_run[ch] = vbase + first;
+            }
           }
         }
 #pragma unroll
@@ -549,18 +581,18 @@ head_train_kernel(const __grid_constant__ CUtensorMap tmap_x,    // x [n, h], bo
         fence_proxy_async();  // the lines are read by the async proxy (bulk copies, MMAs)
         __syncwarp();
         if (lane == 0) {
-          if (writes_own) mbar_arrive(p_in);   // a quarter of the own block of the own buffer
+          if (writes_own) mbar_arrive(p_in(c));   // a quarter of the own block of the own buffer
           mbar_arrive(stage_ready);
         }
         if (copy_warp) {
           if (!mbar_wait_warp(stage_ready, scount & 1u, abort_flag)) return false;
           if (copy_lane) {
             bulk_copy_to_cluster(mapa_shared(own_block, c ^ 2u), own_block, HALF_BYTES,
-                                 mapa_shared(p_in, c ^ 2u));
+                                 mapa_shared(p_in(c), c ^ 2u));
             bulk_copy_to_cluster(mapa_shared(own_block, c ^ 1u), stage_buf, HALF_BYTES,
-                                 mapa_shared(p_in, c ^ 1u));
+                                 mapa_shared(p_in(c), c ^ 1u));
             bulk_copy_to_cluster(mapa_shared(own_block, c ^ 3u), stage_buf, HALF_BYTES,
-                                 mapa_shared(p_in, c ^ 3u));
+                                 mapa_shared(p_in(c), c ^ 3u));
           }
         }
         return true;
@@ -585,12 +617,12 @@ head_train_kernel(const __grid_constant__ CUtensorMap tmap_x,    // x [n, h], bo
         const long long t0 = clock64();
         while (ok && !(stored && drained)) {
           if (!stored &&
-              __all_sync(0xffffffffu, mbar_try_wait_cluster(p_empty, (scount & 1u) ^ 1u))) {
+              __all_sync(0xffffffffu, mbar_test_wait_cluster(p_empty, (scount & 1u) ^ 1u))) {
             ok = hand_over();
             stored = true;
           }
           if (ok && !drained &&
-              __all_sync(0xffffffffu, mbar_try_wait_cluster(s_full, (scount + 1u) & 1u))) {
+              __all_sync(0xffffffffu, mbar_test_wait_cluster(s_full, (scount + 1u) & 1u))) {
             drain_logits();
             drained = true;
           }
@@ -611,8 +643,8 @@ head_train_kernel(const __grid_constant__ CUtensorMap tmap_x,    // x [n, h], bo
         out = p.dx + static_cast<size_t>(rt) * BM * p.h + (hs0 - pcol0);
         out_ld = static_cast<size_t>(p.h);
       } else {
-        out = p.dx_part + (static_cast<size_t>(cluster_id / p.rem_tp) * p.rem_tp +
-                           cluster_id % p.rem_tp) * BM * pass_w;
+        out = p.dx_part + (static_cast<size_t>(cluster_id / split.rem_tp) * split.rem_tp +
+                           cluster_id % split.rem_tp) * BM * pass_w;
         out_ld = static_cast<size_t>(pass_w);
       }
       for (int hb = 0; hb < p.nhb; ++hb) {
@@ -627,7 +659,7 @@ head_train_kernel(const __grid_constant__ CUtensorMap tmap_x,    // x [n, h], bo
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               const int rr = hf * 64 + ch * 32 + j;
-              if (rt * BM + rr < p.n)
+              if (rt * BM + rr < n_rows)
                 out[static_cast<size_t>(rr) * out_ld + ocol] = __uint_as_float(r[j]);
             }
           }
@@ -640,25 +672,26 @@ head_train_kernel(const __grid_constant__ CUtensorMap tmap_x,    // x [n, h], bo
         for (int ch = 0; ch < 2; ++ch) {
           const int rr = hf * 64 + ch * 32 + lane;
           const int row = rt * BM + rr;
-          if (row < p.n) {
+          if (row < n_rows) {
             size_t o;
-            float *ds, *dt;
-            int *dk, *di;
+            float *ds, *dt, *dm;
+            int* di;
             if (direct) {
               o = static_cast<size_t>(slot) * p.n + row;
-              ds = p.st_s; dt = p.st_t; dk = p.st_key; di = p.st_idx;
+              ds = p.st_s; dt = p.st_t; dm = p.st_max; di = p.st_idx;
             } else {
-              const int run = cluster_id / p.rem_tp, j = cluster_id % p.rem_tp;
-              o = (static_cast<size_t>(run) * 16 + slot) * (static_cast<size_t>(p.rem_tp) * BM) +
+              const int run = cluster_id / split.rem_tp, j = cluster_id % split.rem_tp;
+              o = (static_cast<size_t>(run) * 16 + slot) *
+                      (static_cast<size_t>(split.rem_tp) * BM) +
                   static_cast<size_t>(j) * BM + rr;
-              ds = p.lo_s; dt = p.lo_t; dk = p.lo_key; di = p.lo_idx;
+              ds = p.lo_s; dt = p.lo_t; dm = p.lo_max; di = p.lo_idx;
             }
             ds[o] = s_run[ch];
             dt[o] = t_run[ch];
-            dk[o] = k_run[ch];
+            dm[o] = m_run[ch];
             di[o] = i_run[ch];
-            if (k_run[ch] != KEY_NONE &&
-                fmaf(key_float(k_run[ch] & ~31), LOG2E, row_c2[rr]) > OVERFLOW_NATS * LOG2E)
+            // -inf (no vocabulary row in range) and NaN compare false
+            if (fmaf(m_run[ch], LOG2E, row_c2[rr]) > OVERFLOW_NATS * LOG2E)
               atomicExch(p.overflow, 1);
           }
         }
@@ -685,162 +718,5 @@ head_train_kernel(const __grid_constant__ CUtensorMap tmap_x,    // x [n, h], bo
   if (warp == 1) tmem_dealloc_pair(tmem_base, TMEM_COLS);
 }
 
-
-// Finishes one row after the sweep (one block of 128 threads per row):
-//   merges the row's partial statistics (16 slots per vocabulary run; all relative to m_ref, so
-//   sums add and the largest key wins, lowest index on equal keys), writes lse / entropy / argmax /
-//   target logit / ce / masked weight like head_rows_kernel, and turns the raw accumulator into
-//   dHidden in place (exact zeros when cew = 0); the target's own term is added here in fp32.
-//   Raw rows of left-over tiles are the sum of their pieces (fixed order).
-struct TrainRowsParams {
-  int n, h, v;
-  int n_row_tiles, n_clusters, full_rounds, rem_tp, rem_splits, pass_w;
-  const void* x;
-  const void* w;
-  const long long* target;
-  const float* ce_weight;
-  const float* m_ref;
-  const float *st_s, *st_t, *lo_s, *lo_t;
-  const int *st_key, *st_idx, *lo_key, *lo_idx;
-  const float* dx_part;
-  float* dx;
-  float *lse, *tlogit, *ce, *ent, *cew_out;
-  long long* amax;
-};
-
-template <int kFmt>
-__global__ void __launch_bounds__(128) head_train_rows_kernel(const TrainRowsParams q) {
-  __shared__ float sh_f[3][4];
-  __shared__ int sh_k[4], sh_i[4];
-  const int row = blockIdx.x;
-  const int rt = row / 128, rr = row % 128;
-  const int first_tp = q.full_rounds * q.n_clusters;   // first left-over (row tile, pass) pair
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // ---- statistics ---------------------------------------------------------------------------
-  float s = 0.f, t = 0.f;
-  int key = static_cast<int>(0x80000000u), idx = 0x7fffffff;
-  {
-    const bool lo = rt >= first_tp;      // pass 0 of this row tile was swept in vocabulary runs
-    const int nslots = lo ? q.rem_splits * 16 : 16;
-    const size_t stride = lo ? static_cast<size_t>(q.rem_tp) * 128 : static_cast<size_t>(q.n);
-    const size_t o0 = lo ? static_cast<size_t>(rt - first_tp) * 128 + rr : static_cast<size_t>(row);
-    const float* ps = lo ? q.lo_s : q.st_s;
-    const float* pt = lo ? q.lo_t : q.st_t;
-    const int* pk = lo ? q.lo_key : q.st_key;
-    const int* pi = lo ? q.lo_idx : q.st_idx;
-    for (int k = threadIdx.x; k < nslots; k += 128) {
-      const size_t o = o0 + k * stride;
-      s += ps[o];
-      t += pt[o];
-      const int kk = pk[o], ii = pi[o];
-      if ((kk >> 5) > (key >> 5) || ((kk >> 5) == (key >> 5) && ii < idx)) {
-        key = kk;
-        idx = ii;
-      }
-    }
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    s += __shfl_xor_sync(0xffffffffu, s, o);
-    t += __shfl_xor_sync(0xffffffffu, t, o);
-    const int kk = __shfl_xor_sync(0xffffffffu, key, o), ii = __shfl_xor_sync(0xffffffffu, idx, o);
-    if ((kk >> 5) > (key >> 5) || ((kk >> 5) == (key >> 5) && ii < idx)) {
-      key = kk;
-      idx = ii;
-    }
-  }
-  // ---- target logit: x[row, :] . W[target, :] ---------------------------------------------------
-  const long long tg = q.target[row];
-  const bool valid = tg >= 0 && tg < q.v;
-  float tz = 0.f;
-  if (valid)   // h is a multiple of 8: eight 16-bit values (16 bytes) per load
-    for (int c = threadIdx.x * 8; c < q.h; c += 128 * 8) {
-      const float4 xa = load4_16<kFmt>(q.x, (static_cast<size_t>(row) * q.h + c) / 4);
-      const float4 xb = load4_16<kFmt>(q.x, (static_cast<size_t>(row) * q.h + c) / 4 + 1);
-      const float4 wa = load4_16<kFmt>(q.w, (static_cast<size_t>(tg) * q.h + c) / 4);
-      const float4 wb = load4_16<kFmt>(q.w, (static_cast<size_t>(tg) * q.h + c) / 4 + 1);
-      tz = fmaf(xa.x, wa.x, tz);
-      tz = fmaf(xa.y, wa.y, tz);
-      tz = fmaf(xa.z, wa.z, tz);
-      tz = fmaf(xa.w, wa.w, tz);
-      tz = fmaf(xb.x, wb.x, tz);
-      tz = fmaf(xb.y, wb.y, tz);
-      tz = fmaf(xb.z, wb.z, tz);
-      tz = fmaf(xb.w, wb.w, tz);
-    }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) tz += __shfl_xor_sync(0xffffffffu, tz, o);
-  if (lane == 0) {
-    sh_f[0][warp] = s;
-    sh_f[1][warp] = t;
-    sh_f[2][warp] = tz;
-    sh_k[warp] = key;
-    sh_i[warp] = idx;
-  }
-  __syncthreads();
-  s = sh_f[0][0] + sh_f[0][1] + sh_f[0][2] + sh_f[0][3];
-  t = sh_f[1][0] + sh_f[1][1] + sh_f[1][2] + sh_f[1][3];
-  tz = sh_f[2][0] + sh_f[2][1] + sh_f[2][2] + sh_f[2][3];
-  key = sh_k[0];
-  idx = sh_i[0];
-#pragma unroll
-  for (int k = 1; k < 4; ++k)
-    if ((sh_k[k] >> 5) > (key >> 5) || ((sh_k[k] >> 5) == (key >> 5) && sh_i[k] < idx)) {
-      key = sh_k[k];
-      idx = sh_i[k];
-    }
-  const float cw = valid ? q.ce_weight[row] : 0.f;
-  // s, t so far leave out the target entry: add its own term in fp32
-  const float m = q.m_ref[row] + trn::REF_MARGIN;
-  const float s_rest = s;
-  float p_t = 0.f;
-  if (valid) {
-    p_t = __expf(tz - m);
-    s += p_t;
-    t += p_t * (tz - m);
-  }
-  const float log_s = logf(s);
-  const float l = m + log_s;
-  if (threadIdx.x == 0) {
-    q.lse[row] = l;
-    q.ent[row] = log_s - t / s;
-    q.amax[row] = idx;
-    q.tlogit[row] = valid ? tz : 0.f;
-    // ln s - (z_t - m) = ln(1 + s_rest / p_t): the form without cancellation for confident rows
-    q.ce[row] = valid ? (s_rest < p_t ? log1pf(s_rest / p_t) : (l - tz)) : 0.f;
-    q.cew_out[row] = cw;
-  }
-  // ---- dHidden in place:  cew (raw / s - (1 - p_t / s) W[target]),  1 - p_t / s = s_rest / s ----
-  const float inv_s = 1.f / s;
-  const float coef = s_rest * inv_s;
-  float* drow = q.dx + static_cast<size_t>(row) * q.h;
-  for (int c = threadIdx.x * 4; c < q.h; c += 128 * 4) {   // pass widths are multiples of 512
-    float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (cw != 0.f) {
-      const int pass = c / q.pass_w;
-      const int tp = pass * q.n_row_tiles + rt;
-      float4 rawv;
-      if (tp < first_tp) {
-        rawv = *reinterpret_cast<const float4*>(drow + c);
-      } else {
-        const size_t piece = static_cast<size_t>(q.rem_tp) * 128 * q.pass_w;
-        const float* src = q.dx_part + (static_cast<size_t>(tp - first_tp) * 128 + rr) * q.pass_w +
-                           (c - pass * q.pass_w);
-        rawv = *reinterpret_cast<const float4*>(src);
-        for (int k = 1; k < q.rem_splits; ++k) {
-          const float4 b = *reinterpret_cast<const float4*>(src + k * piece);
-          rawv.x += b.x;
-          rawv.y += b.y;
-          rawv.z += b.z;
-          rawv.w += b.w;
-        }
-      }
-      const float4 wt = load4_16<kFmt>(q.w, (static_cast<size_t>(tg) * q.h + c) / 4);
-      val = make_float4(cw * (rawv.x * inv_s - coef * wt.x), cw * (rawv.y * inv_s - coef * wt.y),
-                        cw * (rawv.z * inv_s - coef * wt.z), cw * (rawv.w * inv_s - coef * wt.w));
-    }
-    *reinterpret_cast<float4*>(drow + c) = val;
-  }
-}
 
 }  // namespace esep

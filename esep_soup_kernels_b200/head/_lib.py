@@ -19,8 +19,10 @@ ERR_ALIGNMENT = -6
 ERR_STATIC_SCRATCH = -7
 DTYPE_F16 = 0
 DTYPE_BF16 = 1
+DTYPE_F32 = 2
 RECORD_FIELDS = 5
 METRIC_SCALARS = 4
+STEP_SCALARS = 8
 
 
 class Caps(ctypes.Structure):
@@ -72,6 +74,10 @@ SIGNATURES = {
     "esep_head_train_workspace_bytes": (_SZ, [_I64, _I64, _I64, _INT]),
     "esep_head_train": (_INT, [_P, _P, _P, _P, _P, _I64, _I64, _I64, _INT, _P, _P, _P, _P, _P, _P,
                                _P, _P, _P, _P, _P, _SZ, _P]),
+    "esep_head_step_workspace_bytes": (_SZ, [_I64, _I64, _I64, _INT, _INT]),
+    "esep_head_step": (_INT, [_P, _INT, _P, _P, _INT, _I64, _I64, _I64, _P, _P, _P, _P, _I64, _INT,
+                              _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _SZ, _P]),
+    "esep_head_debug_counters": (_INT, [ctypes.POINTER(ctypes.c_longlong), _INT]),
     "esep_head_norm_forward": (_INT, [_P, _P, _P, _I64, _I64, ctypes.c_float, _INT, _P, _P, _P,
                                       _P]),
     "esep_head_norm_backward": (_INT, [_P, _P, _P, _P, _P, _I64, _I64, _INT, _P, _P, _P]),

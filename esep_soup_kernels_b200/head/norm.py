@@ -85,7 +85,7 @@ class _NormHead(torch.autograd.Function):
     @staticmethod
     def forward(ctx, r_in, delta, norm_weight, w16, target, ce_weight, eps):
         r_out, y, rstd = final_norm_forward(r_in, delta, norm_weight, eps, w16.dtype)
-        loss, stats, dx = _forward(y, w16, target, ce_weight, True)
+        loss, stats, dx, _ = _forward(y, w16, target, ce_weight, True)
         dr, _ = final_norm_backward(dx, r_out, rstd, norm_weight)
         ctx.save_for_backward(dr)
         ctx.delta_dtype = delta.dtype if delta is not None else None
@@ -124,44 +124,9 @@ def fused_norm_linear_ce(r_in, delta, norm_weight, w16, target, ce_weight, eps=1
     else:
         with torch.no_grad():
             _, y, _ = final_norm_forward(r_in, delta, norm_weight, eps, w16.dtype)
-            loss, stats, _ = _forward(y, w16, target, ce_weight, False)
+            loss, stats, _, _ = _forward(y, w16, target, ce_weight, False)
     return loss, dict(zip(_KEYS, stats))
 
 
 __all__ = ["final_norm_forward", "final_norm_backward", "fused_norm_linear_ce"]
 
-
-def _bandwidth_report(rows=65536, hidden=1536, dtype=torch.float16, iters=20):
-    """Times the two kernels on inputs larger than L2 and prints achieved GB/s against the
-    algorithmic bytes (forward 12 H, backward 14 H per row). `python -m ...head.norm [rows hidden]`."""
-    dev = torch.device("cuda", torch.cuda.current_device())
-    r = torch.randn(rows, hidden, device=dev)
-    d = torch.randn(rows, hidden, device=dev).to(dtype)
-    g = torch.rand(hidden, device=dev) + 0.5
-    dy = torch.randn(rows, hidden, device=dev)
-    r_out, _, rstd = final_norm_forward(r, d, g, 1e-6, dtype)
-
-    def timed(fn):
-        for _ in range(3):
-            fn()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(iters):
-            fn()
-        e1.record()
-        torch.cuda.synchronize()
-        return e0.elapsed_time(e1) / iters
-
-    ms_f = timed(lambda: final_norm_forward(r, d, g, 1e-6, dtype))
-    ms_b = timed(lambda: final_norm_backward(dy, r_out, rstd, g, None, dtype))
-    for name, ms, per_row in (("forward", ms_f, 12), ("backward", ms_b, 14)):
-        nbytes = per_row * hidden * rows
-        print(f"final norm {name}: {rows} x {hidden} {dtype}: {ms * 1e3:.1f} us, "
-              f"{nbytes / 1e6:.0f} MB algorithmic, {nbytes / ms / 1e6:.0f} GB/s")
-
-
-if __name__ == "__main__":
-    import sys
-
-    _bandwidth_report(*(int(a) for a in sys.argv[1:3]))

@@ -16,30 +16,28 @@
 As in the reference the input gradient is computed in the forward call when it is needed
 (op.py:15-16, 131-145) and the autograd backward only scales it by grad_loss.
 
-Differences from the reference, all inside the boundary: the logits are never written to memory
-(the 256-row chunk buffer of op.py:83-84 does not exist, so ``chunk_rows`` is accepted and
-ignored); logits stay fp32 in tensor memory instead of being rounded to fp16 (op.py:18, 90), so
-results sit closer to the fp32 oracle. The reference moves the rows that carry a loss to the
-front and reads their count on the host every call (op.py:112-117) so that the gradient pass
-skips ignored rows; here that is done only while it pays: each call leaves its live-row count in
-pinned host memory without waiting for it, and a call compacts the live rows for the backward
-sweep (one host synchronisation, like the reference) only if the call TWO BEFORE it on that device
-had more than COMPACT_DEAD_FRACTION of its rows ignored (a fixed lag: that count has arrived, and
-the choice never depends on timing). Either way ignored and zero-weight rows get
-an exactly zero dHidden.
+One C call (``esep_head_step``) does the whole of op.py:68-128 on the device and is a function of
+its arguments only: masks, the stable "rows with a loss first" order, the row counts and the
+work split of the kernels are all computed on the GPU, the host never waits for a count (the
+reference reads the number of live rows back on every call, op.py:116). Rows that need a
+gradient go through ONE pass over the vocabulary (logits computed once, statistics and dHidden
+from the same tiles); rows that only need statistics (ignored or zero-weight rows when there are
+many of them, every row of a call without gradient) go through a forward sweep. The logits are
+never written to memory (the 256-row chunk buffer of op.py:83-84 does not exist, so
+``chunk_rows`` is accepted and ignored) and stay fp32 in tensor memory instead of being rounded
+to fp16 (op.py:18, 90), so results sit closer to the fp32 oracle.
 
-A call that needs the gradient normally runs the SINGLE-SWEEP training kernel
-(``esep_head_train``): one pass over the vocabulary gives the statistics and dHidden, the logits
-are computed once instead of twice. Its softmax weights are bf16 relative to a reference maximum
-taken from a vocabulary prefix; a row whose true maximum lies more than 60 above that reference
-raises a device flag and the library's guarded two-kernel path (forward sweep + recomputing
-backward sweep, queued behind the flag in the same call) overwrites the outputs - no host
-synchronisation either way. For an fp16 model the dHidden GEMM reads a cached bf16 copy of the
-frozen weight. SINGLE_SWEEP = False, a batch after one with more than SWEEP_DEAD_FRACTION ignored
-rows, or a call without gradient use the two-kernel path directly.
+The single pass takes its softmax weights (bf16) relative to a per-row reference maximum from a
+vocabulary prefix; a row whose true maximum lies more than 115 above its prefix maximum raises a
+device flag and the library's guarded two-kernel path (forward sweep + recomputing backward
+sweep, queued behind the flag in the same call) replaces the results - no host synchronisation
+either way. For an fp16 model the dHidden GEMM reads a cached bf16 copy of the frozen weight
+(V*H*2 bytes of device memory per model). ``SINGLE_SWEEP = False`` makes calls with gradient use
+the two-kernel path directly.
 """
 
 import ctypes
+import threading
 
 import torch
 
@@ -50,24 +48,24 @@ CHUNK_ROWS = 256
 G_SCALE = 1024.0
 VOCAB = 151936
 
-# Backward on the live rows only once the previous call had at least this share of dead rows.
-COMPACT_DEAD_FRACTION = 0.125
-
-# Training calls use the single-sweep kernel (module docstring); False forces the two-kernel path.
+# Calls with gradient use the single pass (module docstring); False = forward sweep + backward
+# sweep over all rows. A switch the caller sets, never something the library infers.
 SINGLE_SWEEP = True
-# ... unless the previous call had more than this share of dead rows: the single sweep does the
-# work of every row (4 H V N), forward on all rows + backward on the live ones costs
-# 2 H V N + 4 H V N_live, which is less from about one third of dead rows on (measured break-even).
-SWEEP_DEAD_FRACTION = 0.35
 
 _KEYS = ("lse", "target_logit", "ce", "entropy", "argmax")
 _DTYPES = {torch.float16: _lib.DTYPE_F16, torch.bfloat16: _lib.DTYPE_BF16}
+_X_DTYPES = {torch.float16: _lib.DTYPE_F16, torch.bfloat16: _lib.DTYPE_BF16,
+             torch.float32: _lib.DTYPE_F32}
+
+# Monitoring only (last_device_status / last_call_fell_back): the workspace of the most recent
+# call per device. Results never depend on it.
+_state_lock = threading.Lock()
 _last_workspace = {}
 _last_overflow = {}
 
 
 def _ptr(t):
-    return ctypes.c_void_p(t.data_ptr())
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else None
 
 
 def _stream(device):
@@ -86,8 +84,15 @@ def warmup(device=None, vocab=VOCAB):
     _lib.check("esep_head_warmup", _lib.load().esep_head_warmup(index))
 
 
+def _remember(device, ws, overflow):
+    with _state_lock:
+        _last_workspace[device.index] = ws
+        _last_overflow[device.index] = overflow
+
+
 class DeviceBackend:
-    """One op call's view of the CUDA library: owns the scratch workspace of the call."""
+    """The C entry points for one problem size, with the scratch workspace they need. Used by the
+    sharded forms (parallel.py) and by the explicit two-kernel path."""
 
     def __init__(self, x16, w16, need_grad):
         self.lib = _lib.load()
@@ -98,16 +103,13 @@ class DeviceBackend:
         with torch.cuda.device(self.device):
             nbytes = self.lib.esep_head_workspace_bytes(self.n, self.h, self.v_local, self.dtype,
                                                         int(need_grad))
-            if need_grad and nbytes:   # room for the single sweep too: one allocation per call
-                nbytes = max(nbytes, self.lib.esep_head_train_workspace_bytes(
-                    self.n, self.h, self.v_local, self.dtype))
         if nbytes == 0:
-            code, caps = _lib.query(self.device.index)
+            code, _ = _lib.query(self.device.index)
             _lib.check("esep_head_query", code)
             raise _lib.HeadLibraryError("esep_head_workspace_bytes", -1, "no plan for this size")
         self.ws = torch.empty(nbytes, device=self.device, dtype=torch.uint8)
         self.ws[:256].zero_()   # device status word (a backward-only call never clears it)
-        _last_workspace[self.device.index] = self.ws
+        _remember(self.device, self.ws, None)
 
     def forward_partial(self, x16, w16, target, vocab_offset=0):
         rec = torch.empty(_lib.RECORD_FIELDS, self.n, device=self.device, dtype=torch.float32)
@@ -120,10 +122,10 @@ class DeviceBackend:
 
     def finalize(self, records, target, ce_weight, v_global):
         n, dev = self.n, self.device
-        f32 = lambda *s: torch.empty(*s, device=dev, dtype=torch.float32)
-        out = {"lse": f32(n), "target_logit": f32(n), "ce": f32(n), "entropy": f32(n),
-               "argmax": torch.empty(n, device=dev, dtype=torch.int64), "cew": f32(n),
-               "loss": f32(1), "metrics": f32(_lib.METRIC_SCALARS)}
+        f = torch.empty(5 * n + 1 + _lib.METRIC_SCALARS, device=dev, dtype=torch.float32)
+        out = {"lse": f[0:n], "target_logit": f[n:2 * n], "ce": f[2 * n:3 * n],
+               "entropy": f[3 * n:4 * n], "cew": f[4 * n:5 * n], "loss": f[5 * n:5 * n + 1],
+               "metrics": f[5 * n + 1:], "argmax": torch.empty(n, device=dev, dtype=torch.int64)}
         k = records.shape[0] if records.dim() == 3 else 1
         with torch.cuda.device(dev):
             code = self.lib.esep_head_finalize(
@@ -137,32 +139,11 @@ class DeviceBackend:
     accepts_out = True   # backward(..., out=) writes dHidden into a caller-owned buffer
 
     def train(self, x16, w16, w_bf16, target, ce_weight):
-        """Single sweep: statistics and dHidden of the full vocabulary in one call. Returns the
-        finalize() dictionary plus "dx" and "overflow" (device int: 1 if the guarded two-kernel
-        path produced the outputs)."""
-        n, dev = self.n, self.device
-        with torch.cuda.device(dev):
-            nbytes = self.lib.esep_head_train_workspace_bytes(n, self.h, self.v_local, self.dtype)
-        if nbytes == 0:
-            raise _lib.HeadLibraryError("esep_head_train_workspace_bytes", -1, "no plan for this size")
-        if self.ws.numel() < nbytes:
-            self.ws = torch.empty(nbytes, device=dev, dtype=torch.uint8)
-            self.ws[:256].zero_()
-            _last_workspace[dev.index] = self.ws
-        f32 = lambda *s: torch.empty(*s, device=dev, dtype=torch.float32)
-        out = {"lse": f32(n), "target_logit": f32(n), "ce": f32(n), "entropy": f32(n),
-               "argmax": torch.empty(n, device=dev, dtype=torch.int64), "cew": f32(n),
-               "loss": f32(1), "metrics": f32(_lib.METRIC_SCALARS), "dx": f32(n, self.h),
-               "overflow": torch.empty(1, device=dev, dtype=torch.int32)}
-        with torch.cuda.device(dev):
-            code = self.lib.esep_head_train(
-                _ptr(x16), _ptr(w16), _ptr(w_bf16), _ptr(target), _ptr(ce_weight), n, self.h,
-                self.v_local, self.dtype, _ptr(out["lse"]), _ptr(out["target_logit"]),
-                _ptr(out["ce"]), _ptr(out["entropy"]), _ptr(out["argmax"]), _ptr(out["cew"]),
-                _ptr(out["loss"]), _ptr(out["metrics"]), _ptr(out["dx"]), _ptr(out["overflow"]),
-                _ptr(self.ws), self.ws.numel(), _stream(dev))
-        _lib.check("esep_head_train", code)
-        _last_overflow[dev.index] = out["overflow"]
+        """Single pass over this weight as a vocabulary of its own: statistics and dHidden of
+        every row. Returns the finalize() dictionary plus "dx" and "overflow" (device int: 1 if
+        the guarded two-kernel path produced the outputs)."""
+        out = _run_step(x16, w16, True, target=target, ce_weight=ce_weight, w_bf16=w_bf16)
+        out["metrics"] = out["metrics"][:_lib.METRIC_SCALARS]
         return out
 
     def backward(self, x16, w16, target, cew, lse, vocab_offset=0, out=None):
@@ -185,7 +166,8 @@ def last_device_status(device=None):
     """Synchronises and returns the device status word of the most recent call on ``device``
     (0 = every kernel ran to completion; see include/esep_head.h). Raises on a non-zero word."""
     index = torch.cuda.current_device() if device is None else torch.device(device).index
-    ws = _last_workspace.get(index)
+    with _state_lock:
+        ws = _last_workspace.get(index)
     if ws is None:
         return 0
     out = ctypes.c_int(0)
@@ -197,12 +179,89 @@ def last_device_status(device=None):
 
 
 def last_call_fell_back(device=None):
-    """True if the most recent single-sweep call on the device raised its overflow flag, i.e. its
+    """True if the most recent single-pass call on the device raised its overflow flag, i.e. its
     outputs came from the guarded two-kernel path. Synchronises (a test / monitoring aid)."""
     device = torch.device("cuda" if device is None else device)
     index = torch.cuda.current_device() if device.index is None else device.index
-    flag = _last_overflow.get(index)
+    with _state_lock:
+        flag = _last_overflow.get(index)
     return bool(flag.item()) if flag is not None else False
+
+
+class _Bf16Copies:
+    """bf16 copy of a frozen 16-bit head weight for the single pass's dHidden GEMM, one entry per
+    device, keyed like the reference's fp16 weight cache (patch.py:93-101: data pointer, shape,
+    dtype, version counter). The entry also HOLDS the source tensor: while it is cached its
+    memory cannot be freed and handed to another tensor, so an equal key always means the same
+    weight (a key on the address alone would match a new tensor that reuses a freed address).
+    Cost: a weight the caller has dropped stays alive until another weight replaces it."""
+
+    def __init__(self):
+        self.lock = threading.Lock()
+        self.entries = {}
+
+    def get(self, w16):
+        if w16.dtype == torch.bfloat16:
+            return w16
+        key = (w16.data_ptr(), tuple(w16.shape), w16.dtype, w16._version)
+        with self.lock:
+            hit = self.entries.get(w16.device.index)
+            if hit is not None and hit[0] == key:
+                return hit[2]
+        with torch.no_grad():
+            copy = w16.detach().to(torch.bfloat16)
+        with self.lock:
+            self.entries[w16.device.index] = (key, w16, copy)
+        return copy
+
+    def clear(self):
+        with self.lock:
+            self.entries.clear()
+
+
+_bf16_copies = _Bf16Copies()
+
+
+def _bf16_weight(w16):
+    return _bf16_copies.get(w16)
+
+
+def _run_step(x, w16, need_grad, target=None, ce_weight=None, labels=None, attention_mask=None,
+              seq_len=0, w_bf16=None):
+    """One ``esep_head_step`` call. x: [m, h] contiguous in w16's dtype or fp32. Flat rows
+    (target, ce_weight) or a [m / seq_len, seq_len] step (labels, attention_mask). Returns a
+    dict of views: the five statistics, "cew", "loss" [1], "metrics" [8], "dx" (or None) and
+    "overflow" (device int32 [1])."""
+    lib = _lib.load()
+    dev = x.device
+    m, h = x.shape
+    v = w16.shape[0]
+    dtype = _DTYPES[w16.dtype]
+    with torch.cuda.device(dev):
+        nbytes = lib.esep_head_step_workspace_bytes(m, h, v, dtype, int(need_grad))
+        if nbytes == 0:
+            code, _ = _lib.query(dev.index)
+            _lib.check("esep_head_query", code)
+            raise _lib.HeadLibraryError("esep_head_step_workspace_bytes", -1, "no plan for this size")
+        ws = torch.empty(nbytes, device=dev, dtype=torch.uint8)
+        f = torch.empty(5 * m + 1 + _lib.STEP_SCALARS, device=dev, dtype=torch.float32)
+        out = {"lse": f[0:m], "target_logit": f[m:2 * m], "ce": f[2 * m:3 * m],
+               "entropy": f[3 * m:4 * m], "cew": f[4 * m:5 * m], "loss": f[5 * m:5 * m + 1],
+               "metrics": f[5 * m + 1:], "argmax": torch.empty(m, device=dev, dtype=torch.int64),
+               "dx": torch.empty(m, h, device=dev, dtype=torch.float32) if need_grad else None}
+        overflow = ws[96:100].view(torch.int32)
+        if need_grad and w_bf16 is None:
+            w_bf16 = _bf16_weight(w16)
+        code = lib.esep_head_step(
+            _ptr(x), _X_DTYPES[x.dtype], _ptr(w16), _ptr(w_bf16), dtype, m, h, v, _ptr(target),
+            _ptr(ce_weight), _ptr(labels), _ptr(attention_mask), int(seq_len), int(need_grad),
+            _ptr(out["lse"]), _ptr(out["target_logit"]), _ptr(out["ce"]), _ptr(out["entropy"]),
+            _ptr(out["argmax"]), _ptr(out["cew"]), _ptr(out["loss"]), _ptr(out["metrics"]),
+            _ptr(out["dx"]), None, _ptr(ws), ws.numel(), _stream(dev))
+    _lib.check("esep_head_step", code)
+    out["overflow"] = overflow
+    _remember(dev, ws, overflow)
+    return out
 
 
 def _prepare(x, w16, target, ce_weight):
@@ -212,99 +271,28 @@ def _prepare(x, w16, target, ce_weight):
     return x16, target, cew
 
 
-class _LiveRowHint:
-    """Share of dead rows (no CE term or zero weight) of an earlier call on a device, delivered
-    through pinned memory. A call reads the count that the call TWO before it posted: that one has
-    practically always arrived (no wait), and taking a fixed lag instead of "whatever has arrived"
-    keeps the choice of path, and with it every output bit, independent of host / GPU timing."""
-
-    SLOTS = 4
-
-    def __init__(self):
-        self.host = torch.zeros(self.SLOTS, dtype=torch.float32).pin_memory()
-        self.pending = []          # (event, slot, total rows), oldest first
-        self.next_slot = 0
-        self.value = 0.0
-
-    def read(self):
-        while len(self.pending) > 1:
-            event, slot, total = self.pending.pop(0)
-            event.synchronize()
-            self.value = 1.0 - float(self.host[slot]) / total if total > 0 else 0.0
-        return self.value
-
-    def post(self, cew_masked):
-        if len(self.pending) >= self.SLOTS - 1:     # never overwrite a slot that is still pending
-            return
-        slot = self.next_slot
-        self.next_slot = (slot + 1) % self.SLOTS
-        # nothing here may touch pageable host memory: such a copy would wait for the stream
-        self.host[slot:slot + 1].copy_((cew_masked != 0).sum().float().reshape(1), non_blocking=True)
-        event = torch.cuda.Event()
-        event.record(torch.cuda.current_stream(cew_masked.device))
-        self.pending.append((event, slot, cew_masked.numel()))
-
-
-_live_hints = {}
-_bf16_copies = {}
-
-
-def _bf16_weight(w16):
-    """bf16 copy of a frozen 16-bit head weight for the single sweep's dHidden GEMM, cached per
-    device and keyed like the reference's fp16 weight cache (patch.py:93-101)."""
-    if w16.dtype == torch.bfloat16:
-        return w16
-    key = (w16.data_ptr(), tuple(w16.shape), w16.dtype, w16._version)
-    hit = _bf16_copies.get(w16.device.index)
-    if hit is None or hit[0] != key:
-        with torch.no_grad():
-            hit = (key, w16.detach().to(torch.bfloat16))
-        _bf16_copies[w16.device.index] = hit
-    return hit[1]
-
-
-def _backward_live_rows(x16, w16, target, cew_masked, lse):
-    """dHidden with the backward sweep restricted to the rows that carry a loss (the reference's
-    live-first ordering, op.py:112-117, 96-100). One host synchronisation (the row count)."""
-    n, h = x16.shape
-    idx = torch.nonzero(cew_masked != 0).squeeze(1)           # synchronises: like op.py:116
-    dx = torch.zeros(n, h, device=x16.device, dtype=torch.float32)
-    if idx.numel() == 0:
-        return dx
-    if idx.numel() == n:
-        be = DeviceBackend(x16, w16, True)
-        return be.backward(x16, w16, target, cew_masked, lse, 0)
-    xl = x16.index_select(0, idx)
-    be = DeviceBackend(xl, w16, True)
-    dxl = be.backward(xl, w16, target.index_select(0, idx), cew_masked.index_select(0, idx),
-                      lse.index_select(0, idx), 0)
-    dx.index_copy_(0, idx, dxl)
-    return dx
+def _two_kernel(x, w16, target, cew):
+    """Forward sweep + recomputing backward sweep over all rows (SINGLE_SWEEP = False)."""
+    x16 = x.to(w16.dtype).contiguous()
+    be = DeviceBackend(x16, w16, True)
+    rec = be.forward_partial(x16, w16, target, 0)
+    out = be.finalize(rec, target, cew, w16.shape[0])
+    out["dx"] = be.backward(x16, w16, target, out["cew"], out["lse"], 0)
+    return out
 
 
 def _forward(x, w16, target, ce_weight, need_grad, chunk_rows=CHUNK_ROWS):
-    """Counterpart of op.py:104-128. Returns (loss, (lse, tlogit, ce, ent, argmax), dx)."""
+    """Counterpart of op.py:104-128. Returns (loss, (lse, tlogit, ce, ent, argmax), dx, metrics)."""
     del chunk_rows  # no chunk buffer exists
-    x16, target, cew = _prepare(x, w16, target, ce_weight)
-    be = DeviceBackend(x16, w16, need_grad)
-    if need_grad and SINGLE_SWEEP:
-        hint = _live_hints.setdefault(x16.device.index, _LiveRowHint())
-        if hint.read() <= SWEEP_DEAD_FRACTION:
-            out = be.train(x16, w16, _bf16_weight(w16), target, cew)
-            hint.post(out["cew"])
-            return out["loss"].reshape(()), tuple(out[k] for k in _KEYS), out["dx"]
-    rec = be.forward_partial(x16, w16, target, 0)
-    out = be.finalize(rec, target, cew, w16.shape[0])
-    dx = None
-    if need_grad:
-        hint = _live_hints.setdefault(x16.device.index, _LiveRowHint())
-        if hint.read() > COMPACT_DEAD_FRACTION:
-            dx = _backward_live_rows(x16, w16, target, out["cew"], out["lse"])
-        else:
-            dx = be.backward(x16, w16, target, out["cew"], out["lse"], 0)
-        hint.post(out["cew"])
+    x = x.contiguous()
+    target = target.to(torch.int64).contiguous()
+    cew = ce_weight.to(torch.float32).contiguous()
+    if need_grad and not SINGLE_SWEEP:
+        out = _two_kernel(x, w16, target, cew)
+    else:
+        out = _run_step(x, w16, need_grad, target=target, ce_weight=cew)
     stats = tuple(out[k] for k in _KEYS)
-    return out["loss"].reshape(()), stats, dx
+    return out["loss"].reshape(()), stats, out["dx"], out["metrics"]
 
 
 class FusedLinearCE(torch.autograd.Function):
@@ -312,11 +300,11 @@ class FusedLinearCE(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, w16, target, ce_weight, chunk_rows):
-        loss, stats, dx = _forward(x, w16, target, ce_weight, True, chunk_rows)
+        loss, stats, dx, metrics = _forward(x, w16, target, ce_weight, True, chunk_rows)
         ctx.save_for_backward(dx)
         ctx.x_dtype = x.dtype
-        ctx.mark_non_differentiable(*stats)
-        return (loss, *stats)
+        ctx.mark_non_differentiable(*stats, metrics)
+        return (loss, *stats, metrics)
 
     @staticmethod
     def backward(ctx, grad_loss, *unused):
@@ -324,11 +312,12 @@ class FusedLinearCE(torch.autograd.Function):
         return (dx * grad_loss).to(ctx.x_dtype), None, None, None, None
 
 
-def fused_linear_ce(x, w16, target, ce_weight, need_grad=None, chunk_rows=CHUNK_ROWS):
-    """loss = sum_i ce_weight_i * CE(x_i @ w16^T, target_i), plus per-token stats (module doc).
-
-    need_grad=None means: grad mode is on and x requires grad (op.py:162-163). Without a gradient
-    only the forward sweep runs. Same checks as the reference (op.py:157-161), widened to bf16."""
+def fused_linear_ce_with_metrics(x, w16, target, ce_weight, need_grad=None,
+                                 chunk_rows=CHUNK_ROWS):
+    """``fused_linear_ce`` plus the scalars the kernels reduce on the way, as a device tensor
+    (no synchronisation): [loss_sum, n_valid, n_correct, entropy_sum over valid rows, ...]
+    (include/esep_head.h: ESEP_STEP_SCALARS). They stand for the sums behind the reference's
+    metric logging (patch.py:582-615); a data-parallel job all-reduces this one tensor."""
     assert x.dim() == 2 and w16.dim() == 2 and x.shape[1] == w16.shape[1], "shape mismatch"
     assert w16.dtype in _DTYPES, "w16 must be fp16 or bf16"
     assert x.dtype in (w16.dtype, torch.float32), "x must be fp32 or match w16's 16-bit dtype"
@@ -342,10 +331,21 @@ def fused_linear_ce(x, w16, target, ce_weight, need_grad=None, chunk_rows=CHUNK_
     if not x.shape[0]:                                        # op.py:166-169
         z = torch.zeros(0, device=x.device, dtype=torch.float32)
         loss = x.float().sum() * 0.0 if need_grad else z.sum()
-        return loss, dict(zip(_KEYS, (z, z, z, z, z.long())))
+        return (loss, dict(zip(_KEYS, (z, z, z, z, z.long()))),
+                torch.zeros(_lib.STEP_SCALARS, device=x.device, dtype=torch.float32))
     if need_grad:
-        loss, *stats = FusedLinearCE.apply(x, w16, target, ce_weight, chunk_rows)
+        loss, *rest = FusedLinearCE.apply(x, w16, target, ce_weight, chunk_rows)
+        stats, metrics = rest[:-1], rest[-1]
     else:
         with torch.no_grad():
-            loss, stats, _ = _forward(x, w16, target, ce_weight, False, chunk_rows)
-    return loss, dict(zip(_KEYS, stats))
+            loss, stats, _, metrics = _forward(x, w16, target, ce_weight, False, chunk_rows)
+    return loss, dict(zip(_KEYS, stats)), metrics
+
+
+def fused_linear_ce(x, w16, target, ce_weight, need_grad=None, chunk_rows=CHUNK_ROWS):
+    """loss = sum_i ce_weight_i * CE(x_i @ w16^T, target_i), plus per-token stats (module doc).
+
+    need_grad=None means: grad mode is on and x requires grad (op.py:162-163). Without a gradient
+    only the forward sweep runs. Same checks as the reference (op.py:157-161), widened to bf16."""
+    loss, stats, _ = fused_linear_ce_with_metrics(x, w16, target, ce_weight, need_grad, chunk_rows)
+    return loss, stats

@@ -41,12 +41,17 @@ enum {
 
 #define ESEP_DTYPE_F16 0
 #define ESEP_DTYPE_BF16 1
+#define ESEP_DTYPE_F32 2 /* only as the type of x in esep_head_step (cast to W's type inside) */
 
 /* Number of floats per row in a partial record: max, sum-exp, sum-exp*(z-max), target logit,
  * index of the max (an int32 stored bit-for-bit in the float slot). Layout is [5][n]. */
 #define ESEP_RECORD_FIELDS 5
 /* Scalars written by esep_head_finalize: loss_sum, n_valid, n_correct, entropy_sum(valid rows). */
 #define ESEP_METRIC_SCALARS 4
+/* Scalars written by esep_head_step: the four above, then n_labelled (target != -100),
+ * n_attended rows (attention mask != 0; all rows without a mask), entropy_sum(attended rows),
+ * n_live (rows that took part in the gradient). */
+#define ESEP_STEP_SCALARS 8
 
 typedef struct esep_head_caps {
   int cc_major;
@@ -165,30 +170,56 @@ int esep_head_forward_static(const void* x, const void* w, const int64_t* target
                              int64_t* argmax, float* cew_out, float* loss, float* metrics,
                              void* stream);
 
-/* ---- single-sweep training call ------------------------------------------------------------- */
+/* ---- whole head step: one call, no host synchronisation -------------------------------------- */
 
-/* Bytes of scratch esep_head_train needs for this problem on the current device (0 on error). */
+/* Bytes of scratch esep_head_step needs for m rows on the current device (0 on error). */
+size_t esep_head_step_workspace_bytes(int64_t m, int64_t h, int64_t v, int dtype, int need_grad);
+
+/* Loss, per-row statistics and (need_grad != 0) dHidden of m rows of x against the whole
+ * vocabulary, with everything the reference does around its chunk loop done on the device:
+ *   - masks: a target outside [0, v) means "no CE term", its weight is forced to 0;
+ *   - row classes: rows that carry a loss term with a non-zero weight get their gradient from ONE
+ *     pass over the vocabulary (logits computed once: 4*H*V flops per such row); the other
+ *     selected rows only get statistics from a forward sweep (2*H*V flops per row). The stable
+ *     "live rows first" order, the row counts and the work split of both sweeps are computed on
+ *     the device; the host never waits for a count (the reference reads it back every call);
+ *   - outputs are written at the caller's row index: lse / entropy / argmax for every selected
+ *     row, target_logit / ce 0 where there is no CE term, dx (fp32 [m, h], already multiplied by
+ *     the masked weight) exactly 0 on rows without a gradient.
+ * Two ways to describe the rows:
+ *   flat (labels == NULL):  target[m], ce_weight[m] (NULL = weight 1), every row selected.
+ *   step (labels != NULL):  labels[m] and attention_mask[m] (or NULL) of a [m / seq_len, seq_len]
+ *     batch: target of position t is labels[t + 1] (-100 past the end), weight 1 on targets other
+ *     than -100, a row is selected when it is attended or has a target; rows that are not
+ *     selected get 0 in every output (ce / entropy are then the [B, T] per-token loss / entropy).
+ * x is [m, h] in W's 16-bit type (x_dtype == dtype) or fp32 (x_dtype == ESEP_DTYPE_F32, cast
+ * inside). w_bf16: a bf16 copy of W for the dHidden GEMM (pass w itself for bf16 models; may be
+ * NULL when need_grad == 0). metrics[ESEP_STEP_SCALARS] and overflow may be NULL.
+ * overflow: device int, 1 if a row's largest logit lay more than 115 above its maximum over the
+ * first 2048 vocabulary rows; the two-kernel path (esep_head_forward + esep_head_backward), which
+ * this call always queues behind that flag, then replaced the sweep's results.
+ * Replaces: solution/head/op.py:68-128 (_run, _forward) and the row handling of
+ * solution/head/patch.py:443-487 (label shift, row gather, scatter to [B, T], counters). */
+int esep_head_step(const void* x, int x_dtype, const void* w, const void* w_bf16, int dtype,
+                   int64_t m, int64_t h, int64_t v, const int64_t* target, const float* ce_weight,
+                   const int64_t* labels, const int64_t* attention_mask, int64_t seq_len,
+                   int need_grad, float* lse, float* target_logit, float* ce, float* entropy,
+                   int64_t* argmax, float* cew_out, float* loss, float* metrics, float* dx,
+                   int* overflow, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Older spelling of the flat training call: esep_head_step with target / ce_weight, a gradient
+ * and the first four scalars. Same results. */
 size_t esep_head_train_workspace_bytes(int64_t n, int64_t h, int64_t v, int dtype);
-
-/* Statistics AND dHidden of one training step from a single pass over the vocabulary: the logits
- * tiles are computed once (4*H*V*N flops executed instead of the 6*H*V*N of esep_head_forward +
- * esep_head_backward). Same outputs as esep_head_forward plus dx[n, h] (fp32, already multiplied
- * by the masked weight; exact zeros on ignored / zero-weight rows). Single GPU, full vocabulary.
- *   w_bf16: a bf16 copy of W (the dHidden GEMM runs in bf16 because its softmax operand must be
- *           bf16, see below); pass `w` itself when dtype is ESEP_DTYPE_BF16.
- *   overflow: device int, written by the call. The softmax weights are taken relative to the row
- *           maximum over the first 2048 vocabulary rows; a row whose true maximum is more than 115
- *           above that prefix maximum sets *overflow = 1, and the two-kernel path
- *           (esep_head_forward + esep_head_backward), which this call always queues behind the
- *           flag, then overwrites every output. No host synchronisation either way; the flag is
- *           only informative for the caller.
- * Replaces: the whole chunk body of solution/head/op.py:87-100 (GEMM1, row kernel passes 1 and 2,
- * GEMM2, scale) for the training specialisation, plus op.py:105-108,125-127. */
 int esep_head_train(const void* x, const void* w, const void* w_bf16, const int64_t* target,
                     const float* ce_weight, int64_t n, int64_t h, int64_t v, int dtype, float* lse,
                     float* target_logit, float* ce, float* entropy, int64_t* argmax,
                     float* cew_out, float* loss, float* metrics, float* dx, int* overflow,
                     void* workspace, size_t workspace_bytes, void* stream);
+
+/* Counters for tests: out[0] = per-device initialisations performed so far (function attributes,
+ * occupancy queries), out[1] = tensor maps encoded so far (maps are cached by address and
+ * shape). A warmed-up process that repeats a call sees neither number move. */
+int esep_head_debug_counters(long long* out, int n);
 
 /* ---- the step either side of the head: final residual add + RMSNorm ------------------------- */
 

@@ -297,25 +297,34 @@ def shard_dx(x, w_shard, target, cew, lse, vocab_offset=0, rows_per_step=256):
 # ---------------------------------------------------------------------------------------------
 # solution/head/patch.py:562-579 (_step_from_logits): the per-token results from full logits.
 # ---------------------------------------------------------------------------------------------
-def step_from_logits(hidden, w, labels):
+def step_from_logits(hidden, w, labels, want_grad=False):
     """hidden [B,T,H], w [V,H], labels [B,T] -> dict(token_loss [B,T], token_entropy [B,T],
     correct, labelled, loss_mean): logits = hidden @ w^T in fp32, labels padded with -100 on the
-    right and shifted by one, CE with ignore_index, entropy of every position, argmax accuracy."""
+    right and shifted by one, CE with ignore_index, entropy of every position, argmax accuracy.
+    want_grad adds "dhidden": the gradient of loss_mean with respect to hidden (fp32)."""
     import torch.nn.functional as F
 
     bsz, seq = labels.shape
-    logits = hidden.float() @ w.float().T
+    h32 = hidden.float().detach().requires_grad_(want_grad)
+    logits = h32 @ w.float().T
     vocab = logits.shape[-1]
     target = F.pad(labels, (0, 1), value=IGNORE_INDEX)[:, 1:]
     valid = target != IGNORE_INDEX
     token_loss = F.cross_entropy(logits.reshape(-1, vocab), target.reshape(-1),
                                  ignore_index=IGNORE_INDEX, reduction="none").view(bsz, seq)
     token_loss = torch.where(valid, token_loss, torch.zeros(()))
-    logp = torch.log_softmax(logits, dim=-1)
-    token_entropy = -(logp.exp() * logp).sum(-1)
-    correct = ((logits.argmax(dim=-1) == target) & valid).sum()
-    return {"token_loss": token_loss, "token_entropy": token_entropy, "correct": int(correct),
-            "labelled": int(valid.sum()), "loss_mean": float(token_loss.sum() / valid.sum())}
+    loss_mean = token_loss.sum() / valid.sum()
+    out = {}
+    if want_grad:
+        out["dhidden"] = torch.autograd.grad(loss_mean, h32)[0]
+    with torch.no_grad():
+        logp = torch.log_softmax(logits, dim=-1)
+        token_entropy = -(logp.exp() * logp).sum(-1)
+        correct = ((logits.argmax(dim=-1) == target) & valid).sum()
+    out.update({"token_loss": token_loss.detach(), "token_entropy": token_entropy,
+                "correct": int(correct), "labelled": int(valid.sum()),
+                "loss_mean": float(loss_mean)})
+    return out
 
 
 # ---------------------------------------------------------------------------------------------
