@@ -1,20 +1,30 @@
 """Benchmark of the fused LM head (forward + backward) on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config c2]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-One "step" = one forward + backward pass of the head over one batch of synthetic rows
-(BASELINE configuration 2 by default: 8 unpadded sequences of U[128,1024] rows, fp16, hidden 1536,
-vocabulary 151936). With N > 1 (launched by torch.distributed.run, one rank per GPU) every rank
-processes its own batch of the same shape with the weight replicated, and the ranks exchange one
-4-scalar NCCL all-reduce per step: weak scaling, no data-path collective.
-Prints ONE JSON line on rank 0.
+One "step" = one forward + backward pass of the head over one batch of synthetic rows: 8 unpadded
+sequences of U[128,1024] rows (4 340 rows), fp16, hidden 1536, vocabulary 151 936 - the
+Qwen2.5-1.5B training-step head the metric is quoted on. Prints ONE JSON line on rank 0.
 
---impl reference times the CPU restatement of the reference's full-vocabulary cross-entropy
-(oracle/head_oracle.py, solution/test_head.py:12-51) on the host cores, on a bounded sample of
-the same workload.
+With N > 1 (launched by torch.distributed.run, one rank per GPU):
+  * `value` is weak scaling of that step: every rank processes its own batch of the same shape,
+    the weight is replicated, the ranks exchange one 8-scalar NCCL all-reduce per step;
+  * `strong_c3` times the token-sharded form on 16 384 bf16 rows split evenly over the ranks
+    (strong scaling, same exchange) next to the same rows on one GPU;
+  * `vocab_parallel_c4` times the vocabulary-sharded form on the 7B shape (32 768 rows x 3584 x
+    152 064, bf16, W split by vocabulary rows over the ranks): an all-gather of one [5, rows]
+    record per rank and an all-reduce of dHidden;
+  * both carry a `parity` block: a seeded 64-row subset against the CPU oracle, computed outside
+    every timed region.
+
+--impl reference times the reference's CPU path for this computation (the full-vocabulary
+cross-entropy of solution/test_head.py:12-51, restated in oracle/head_oracle.py) on the host
+cores: every step is one pass over the same batch.
 """
 
 import argparse
+import ctypes
+import importlib.util
 import json
 import os
 import statistics
@@ -48,8 +58,18 @@ def _traffic(kernel):
         return json.load(f).get(kernel)
 
 
+def _synthetic():
+    """The workload generator, loaded by file so that the CPU arm never imports the package
+    (whose import maps the CUDA library)."""
+    path = os.path.join(ROOT, "esep_soup_kernels_b200", "head", "synthetic.py")
+    spec = importlib.util.spec_from_file_location("esep_bench_synthetic", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
 
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -101,91 +121,151 @@ class ClockSampler:
                 "reasons": sorted(reasons)}
 
 
-def _workload(name, seed):
-    from esep_soup_kernels_b200.head.synthetic import make_config
-
-    return make_config(name, seed=seed)
-
-
-def _describe(cfg, n_gpus):
-    m = cfg["meta"]
-    return {"workload": f"{m['name']}: {m['n']} rows x hidden {m['h']} x vocab {m['v']} per GPU, "
-                        f"{m['dtype']}, synthetic (seeded N(0,1) hidden, N(0,0.02) W, uniform labels)",
-            "rows_per_gpu": m["n"], "hidden": m["h"], "vocab": m["v"], "parallelism": f"dp{n_gpus}",
+def _describe(meta, n_gpus):
+    return {"workload": f"{meta['name']}: {meta['n']} rows x hidden {meta['h']} x vocab {meta['v']} "
+                        f"per GPU, {meta['dtype']}, synthetic (seeded N(0,1) hidden, N(0,0.02) W, "
+                        "uniform labels, last token of each of the 8 sequences ignored)",
+            "rows_per_gpu": meta["n"], "hidden": meta["h"], "vocab": meta["v"],
+            "parallelism": f"dp{n_gpus}",
             "l2": "W (467 MB) is larger than the 126 MB L2 and is re-streamed every step; no flush"}
 
 
-def cpu_reference_rate(cfg, budget_s=12.0):
-    """Rows/s of the oracle's full-vocabulary cross-entropy (fwd + dX) on the host cores."""
+# ---------------------------------------------------------------------------------------------
+# CPU arm
+# ---------------------------------------------------------------------------------------------
+def cpu_pass(ho, cfg, rows):
+    """One pass of the oracle's full-vocabulary cross-entropy (fwd + dX) over the first `rows`
+    rows of the batch on all host cores. Returns seconds."""
+    x, w, t, c = cfg["x"], cfg["w"], cfg["target"], cfg["ce_weight"]
+    x16 = x.to(w.dtype)
+    t0 = time.perf_counter()
+    ho.full_vocab_reference(x16[:rows], w, t[:rows], c[:rows], want_rounded=False)
+    return time.perf_counter() - t0
+
+
+def cpu_sample_rows(ho, cfg, budget_s):
+    """Rows of the batch one CPU step passes over: the whole batch if a pass fits the budget."""
+    n = cfg["x"].shape[0]
+    cpu_pass(ho, cfg, min(32, n))                      # thread pool, page faults
+    probe = min(256, n)
+    dt = cpu_pass(ho, cfg, probe)
+    rows = int(min(n, max(probe, probe * budget_s / max(dt, 1e-3))))
+    return rows
+
+
+def cpu_baseline_block(cfg, budget_s=15.0):
+    """The bounded CPU sample beside a GPU run: passes over the batch for about `budget_s`."""
     from oracle import head_oracle as ho
 
     torch.set_num_threads(os.cpu_count() or 1)
-    x, w, t, c = cfg["x"], cfg["w"], cfg["target"], cfg["ce_weight"]
-    x16 = x.to(w.dtype)
-    n = x.shape[0]
-    warm = min(32, n)
-    ho.full_vocab_reference(x16[:warm], w, t[:warm], c[:warm], want_rounded=False)  # thread pool, pages
-    probe = min(256, n)
-    t0 = time.perf_counter()
-    ho.full_vocab_reference(x16[:probe], w, t[:probe], c[:probe], want_rounded=False)
-    dt = time.perf_counter() - t0
-    rows = int(max(probe, min(n, 16384, probe * budget_s / max(dt, 1e-3))))
-    # a batch that takes less than the budget is passed over several times
-    passes = max(1, int(budget_s / max(dt * rows / probe, 1e-3))) if rows == n else 1
-    t0 = time.perf_counter()
-    for _ in range(passes):
-        ho.full_vocab_reference(x16[:rows], w, t[:rows], c[:rows], want_rounded=False)
-    dt = time.perf_counter() - t0
-    rows *= passes
-    return rows / dt, rows, dt
+    rows = cpu_sample_rows(ho, cfg, budget_s / 3)
+    total, secs, passes = 0, 0.0, 0
+    while secs < budget_s * 0.8 and passes < 8:
+        secs += cpu_pass(ho, cfg, rows)
+        total += rows
+        passes += 1
+    return {"value": total / secs, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{passes} pass(es) over the first {rows} of the {cfg['x'].shape[0]} rows, "
+                      f"fwd+dX, {secs:.1f} s"}
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    cfg = _workload(args.config, seed=0)
-    rates = []
-    sample = None
-    for _ in range(max(1, min(args.steps, 3))):
-        r, rows, dt = cpu_reference_rate(cfg, budget_s=8.0)
-        rates.append(r)
-        sample = (f"{rows} rows (passes over the first rows of the {cfg['meta']['n']}-row batch), "
-                  f"fwd+dX, {dt:.1f} s")
-    value = statistics.median(rates)
+    sys.path.insert(0, ROOT)
+    from oracle import head_oracle as ho
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    cfg = _synthetic().make_config("c2", seed=0)
+    meta = cfg["meta"]
+    # every step = one pass over the same rows; the whole batch unless that would take the run
+    # past a few minutes
+    rows = cpu_sample_rows(ho, cfg, budget_s=150.0 / max(1, args.steps + args.warmup))
+    for _ in range(args.warmup):
+        cpu_pass(ho, cfg, rows)
+    secs = [cpu_pass(ho, cfg, rows) for _ in range(args.steps)]
+    per_step = sum(secs) / len(secs)
+    value = rows / per_step
     cores = torch.get_num_threads()
+    sample = (f"each step = one fwd+dX pass over {'all' if rows == meta['n'] else 'the first'} "
+              f"{rows} of the {meta['n']} rows; {args.steps} timed steps, {sum(secs):.1f} s")
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": cfg["meta"]["n"] / value * 1e3,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32",
-            "data": "synthetic", "config": _describe(cfg, args.gpus),
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step * 1e3,
+            "rows_per_step": rows, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
+            "config": _describe(meta, args.gpus),
             "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
                              "sample": sample},
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-            "gpu_launches": 0}
+            "gpu_launches": 0,
+            "note": "one host, whatever --gpus says: the CPU path does not scale with the number of "
+                    "GPUs, so a ratio against it means something at N = 1 only"}
     print(json.dumps(line))
+
+
+# ---------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------
+def _counters():
+    from esep_soup_kernels_b200.head import _lib
+
+    buf = (ctypes.c_longlong * 3)()
+    _lib.load().esep_head_debug_counters(buf, 3)
+    return buf[0], buf[1], buf[2]
+
+
+def _parity(x, w, t, c, loss_terms, stats, dx, rows):
+    """Largest deviations of `rows` from the CPU oracle (fp32 full-vocabulary cross-entropy)."""
+    from oracle import head_oracle as ho
+
+    ref = ho.full_vocab_reference(x[rows], w, t[rows], c[rows], want_rounded=False)
+    got = {k: v[rows].float().cpu() if k != "argmax" else v[rows].cpu() for k, v in stats.items()}
+    z = None
+    miss = got["argmax"] != ref["argmax"]
+    tie_ok = True
+    if bool(miss.any()):   # a different index is fine only where the logits tie
+        z = x[rows][miss].float() @ w.float().T
+        at = z.gather(1, got["argmax"][miss][:, None]).squeeze(1)
+        tie_ok = bool(((z.max(1).values - at).abs() <= 2e-3).all())
+    dxr = dx[rows].float().cpu()
+    ref_loss = float(ref["loss"])
+    return {"rows": int(len(rows)),
+            "loss_rel": abs(float(loss_terms[rows].sum()) - ref_loss) / max(abs(ref_loss), 1e-30),
+            "lse_max_abs": float((got["lse"] - ref["lse"]).abs().max()),
+            "entropy_max_abs": float((got["entropy"] - ref["ent"]).abs().max()),
+            "argmax_equal": float((~miss).float().mean()), "argmax_ok_except_ties": tie_ok,
+            "dx_rel_fro": float((dxr - ref["dx"]).norm() / ref["dx"].norm()),
+            "tolerance": "loss, entropy 1e-3 relative; dHidden 2e-2 relative; argmax exact "
+                         "except ties"}
 
 
 def run_ours(args):
     import torch.distributed as dist
 
-    from esep_soup_kernels_b200.head import fused_linear_ce, last_device_status, warmup
-    from esep_soup_kernels_b200.head.op import DeviceBackend, _prepare
+    sys.path.insert(0, ROOT)
+    from esep_soup_kernels_b200.head import (_lib, fused_linear_ce_with_metrics,
+                                             last_device_status, warmup)
+    from esep_soup_kernels_b200.head import op as head_op
+    from esep_soup_kernels_b200.head import parallel as par
+    from esep_soup_kernels_b200.head.synthetic import (QWEN_1P5B, QWEN_7B, make_config,
+                                                       make_weight)
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+        os.environ["NCCL_DEBUG"] = "WARN"      # keep NCCL's version banner off stdout: one JSON line
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     warmup(dev)
 
-    cfg = _workload(args.config, seed=rank)
+    cfg = make_config("c2", seed=rank)
     meta = cfg["meta"]
     if rank:   # W is replicated: every rank holds the weight of seed 0
-        from esep_soup_kernels_b200.head.synthetic import QWEN_1P5B, QWEN_7B, make_weight
-        std = (QWEN_7B if meta["name"] == "c4" else QWEN_1P5B)["w_std"]
-        cfg["w"] = make_weight(meta["v"], meta["h"], std, cfg["w"].dtype, 0)
+        cfg["w"] = make_weight(meta["v"], meta["h"], QWEN_1P5B["w_std"], cfg["w"].dtype, 0)
     n, h, v = meta["n"], meta["h"], meta["v"]
     x_host = cfg["x"].pin_memory()
     t_host = cfg["target"].pin_memory()
@@ -195,24 +275,27 @@ def run_ours(args):
     tgt = t_host.to(dev)
     cew = c_host.to(dev)
     n_live = int((cfg["ce_weight"] != 0).sum())
-    metrics = torch.zeros(4, device=dev)
     # every rank draws its own batch (same sequence lengths, own values): count the rows of all ranks
     rows_all = torch.tensor([float(n)], device=dev)
     if world > 1:
         dist.all_reduce(rows_all)
     total_rows = rows_all.item()
+    call_events = []    # (start, end) CUDA events around the library call of a step
 
-    def step_device():
+    def step_device(record=False):
         xg = x.detach().requires_grad_(True)
-        loss, stats = fused_linear_ce(xg, w, tgt, cew)
+        if record:
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+        loss, stats, m = fused_linear_ce_with_metrics(xg, w, tgt, cew)
+        if record:
+            b.record()
+            call_events.append((a, b))
         loss.backward()
         if world > 1:
-            m = torch.stack([loss.detach(), (tgt >= 0).sum().float(),
-                             ((stats["argmax"] == tgt) & (tgt >= 0)).sum().float(),
-                             stats["entropy"].sum()])
-            dist.all_reduce(m)
-            metrics.copy_(m)
-        return loss, xg.grad
+            m = m.clone()
+            dist.all_reduce(m)      # the one exchange of a data-parallel step: eight scalars
+        return loss, xg.grad, m
 
     def sync_all():
         torch.cuda.synchronize()
@@ -235,12 +318,22 @@ def run_ours(args):
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return ms.item() / steps
 
+    # ---- the timed region: K steps, inputs resident; the library call of every step is also
+    #      bracketed by its own event pair, so the dominant kernel is timed inside this loop ----
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
         time.sleep(0.3)
-    ms_step = timed(step_device, args.steps, args.warmup)
+    launches0 = _counters()[2]
+    for _ in range(args.warmup):
+        step_device()
+    launches_warm = _counters()[2]
+    ms_step = timed(lambda: step_device(record=True), args.steps, 0)
+    launches1 = _counters()[2]
     clocks = sampler.stop() if rank == 0 else None
+    ms_call = statistics.mean(a.elapsed_time(b) for a, b in call_events)
+    own_launches = launches1 - launches_warm
+    del launches0
 
     # ---- end to end through the public op with HOST inputs --------------------------------
     loss_host = torch.zeros(1).pin_memory()
@@ -249,7 +342,7 @@ def run_ours(args):
         x.copy_(x_host, non_blocking=True)
         tgt.copy_(t_host, non_blocking=True)
         cew.copy_(c_host, non_blocking=True)
-        loss, _ = step_device()
+        loss, _, _ = step_device()
         loss_host.copy_(loss.detach().reshape(1), non_blocking=True)
         torch.cuda.current_stream().synchronize()   # the trainer reads the loss every step
 
@@ -257,45 +350,63 @@ def run_ours(args):
     h2d = x_host.numel() * x_host.element_size() + t_host.numel() * 8 + c_host.numel() * 4
     d2h = 4
 
-    # ---- the two sweeps timed separately (CUDA events on the launching stream) --------------
-    x16, t64, c32 = _prepare(x, w, tgt, cew)
-    be = DeviceBackend(x16, w, True)
-    rec = be.forward_partial(x16, w, t64, 0)
-    fin = be.finalize(rec, t64, c32, v)
+    peaks = _peaks()
+    hv = float(h) * v
+    f_alg = 2.0 * hv * n + 2.0 * hv * n_live
+    line_extra = {}
 
-    def timed_kernel(fn, iters):
-        evs = []
-        for _ in range(3):
-            fn()
-        torch.cuda.synchronize()
-        for _ in range(iters):
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
-            fn()
-            b.record()
-            evs.append((a, b))
-        torch.cuda.synchronize()
-        return statistics.mean(a.elapsed_time(b) for a, b in evs)
+    if world == 1:
+        # ---- sustained: the same step for at least two seconds, clocks sampled meanwhile ----
+        sus_steps = max(50, int(2200.0 / ms_step))
+        s2 = ClockSampler(local)
+        s2.start()
+        time.sleep(0.2)
+        ms_sus = timed(step_device, sus_steps, 0)
+        sus_clocks = s2.stop()
+        sus_tf = f_alg / (ms_sus * 1e-3) / 1e12
+        line_extra["sustained"] = {
+            "steps": sus_steps, "seconds": sus_steps * ms_sus * 1e-3, "ms_per_step": ms_sus,
+            "tokens_s": n / (ms_sus * 1e-3), "achieved_tflops": sus_tf,
+            "peak_sustained": peaks["tflops_sustained"],
+            "frac_of_sustained": sus_tf / peaks["tflops_sustained"],
+            "frac_of_burst": sus_tf / peaks["tflops"], "clocks": sus_clocks}
 
-    iters = max(5, args.steps)
-    ms_fwd = timed_kernel(lambda: be.forward_partial(x16, w, t64, 0), iters)
-    ms_bwd = timed_kernel(lambda: be.backward(x16, w, t64, fin["cew"], fin["lse"], 0), iters)
-    from esep_soup_kernels_b200.head.op import _bf16_weight
-    w_g2 = _bf16_weight(w)
+        # ---- the two-kernel path's sweeps, each timed alone ----------------------------------
+        x16, t64, c32 = head_op._prepare(x, w, tgt, cew)
+        be = head_op.DeviceBackend(x16, w, True)
+        rec = be.forward_partial(x16, w, t64, 0)
+        fin = be.finalize(rec, t64, c32, v)
 
-    def timed_loop(fn, iters):   # one event pair around the loop: the host runs ahead of the GPU
-        for _ in range(3):
-            fn()
-        torch.cuda.synchronize()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(iters):
-            fn()
-        b.record()
-        torch.cuda.synchronize()
-        return a.elapsed_time(b) / iters
+        def timed_kernel(fn, iters):
+            evs = []
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            for _ in range(iters):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                fn()
+                b.record()
+                evs.append((a, b))
+            torch.cuda.synchronize()
+            return statistics.mean(a.elapsed_time(b) for a, b in evs)
 
-    ms_trn = timed_loop(lambda: be.train(x16, w, w_g2, t64, c32), iters)
+        ms_fwd = timed_kernel(lambda: be.forward_partial(x16, w, t64, 0), 10)
+        ms_bwd = timed_kernel(lambda: be.backward(x16, w, t64, fin["cew"], fin["lse"], 0), 10)
+        fwd_tf = 2.0 * hv * n / (ms_fwd * 1e-3) / 1e12
+        bwd_tf = 2.0 * hv * n_live / (ms_bwd * 1e-3) / 1e12
+        line_extra["roofline_two_kernel_path"] = {
+            "head_fwd_kernel": {"achieved": fwd_tf, "frac": fwd_tf / peaks["tflops"], "ms": ms_fwd,
+                                "traffic": _traffic("head_fwd_kernel")},
+            "head_bwd_kernel": {"achieved": bwd_tf, "frac": bwd_tf / peaks["tflops"], "ms": ms_bwd,
+                                "executed_tflops": 4.0 * hv * n / (ms_bwd * 1e-3) / 1e12,
+                                "traffic": _traffic("head_bwd_kernel")},
+            "note": "the forward sweep also serves rows without a gradient; the pair is the guarded "
+                    "second attempt of the single pass and the SINGLE_SWEEP = False path"}
+    else:
+        line_extra["strong_c3"] = _strong_c3(dist, par, make_config, dev, rank, world, peaks, args)
+        line_extra["vocab_parallel_c4"] = _vocab_parallel_c4(dist, par, make_config, make_weight,
+                                                             QWEN_7B, dev, rank, world, peaks, args)
     status = last_device_status(dev)
 
     if world > 1:
@@ -305,69 +416,155 @@ def run_ours(args):
             dist.destroy_process_group()
         return
 
-    from esep_soup_kernels_b200.head import _lib
     _, caps = _lib.query(local)
     pl = _lib.plan_problem(n, h, v, True, caps.sm_count, caps.max_clusters_bwd)
-    # single sweep: prefix fwd sweep, record merge, training sweep, row finish, scalars; then the
-    # guarded two-kernel path, whose kernels return at once unless a row overflowed: fwd sweep,
-    # record merge, row outputs, scalars, bwd sweep (+ partial-dX sum when split)
-    launches_per_step = 5 + 5 + (1 if pl.bwd_rem_pairs > 0 else 0)
-    peaks = _peaks()
-    hv = float(h) * v
-    f_alg_fwd = 2.0 * hv * n
-    f_alg_bwd = 2.0 * hv * n_live
-    f_exec_bwd = 4.0 * hv * n           # logits recompute + dX GEMM, every row of every tile
     tokens_s = total_rows / (ms_step * 1e-3)
-    bwd_tf = f_alg_bwd / (ms_bwd * 1e-3) / 1e12
-    fwd_tf = f_alg_fwd / (ms_fwd * 1e-3) / 1e12
-    trn_tf = (f_alg_fwd + f_alg_bwd) / (ms_trn * 1e-3) / 1e12
+    call_tf = f_alg / (ms_call * 1e-3) / 1e12
     line = {
         "metric": METRIC, "value": tokens_s, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": meta["dtype"], "data": "synthetic",
-        "config": _describe(cfg, world),
+        "config": _describe(meta, world),
         "e2e": {"value": total_rows / (ms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e,
                 "note": "x, labels and weights copied from pinned host memory every step; the LM-head "
                         "weight W is a resident model parameter; loss read back every step"},
-        "gpu_launches": args.steps * launches_per_step,
+        "gpu_launches": own_launches,
+        "gpu_launches_note": "kernels launched by libesep_head.so inside the timed region, counted "
+                             "by the library itself (its counter covers every entry point); torch "
+                             "adds the gradient scaling of the autograd backward and, with N > 1, "
+                             "NCCL's all-reduce",
         "clocks": clocks,
-        "roofline": {"bound": "tensor", "kernel": "head_train_kernel", "achieved": trn_tf,
-                     "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": trn_tf / peaks["tflops"],
+        "roofline": {"bound": "tensor", "kernel": "head_train_kernel", "achieved": call_tf,
+                     "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": call_tf / peaks["tflops"],
                      "traffic": _traffic("head_train_kernel"),
                      "peak_source": peaks["source"] + " burst",
                      "flops": "algorithmic 2*H*V*N + 2*H*V*N_live (logits GEMM + dHidden GEMM, each "
-                              "once); the single sweep executes 4*H*V*N",
-                     "executed_tflops": 4.0 * hv * n / (ms_trn * 1e-3) / 1e12, "ms": ms_trn,
-                     "peak_sustained": peaks["tflops_sustained"],
-                     "frac_of_sustained": trn_tf / peaks["tflops_sustained"],
-                     "ms_note": "the whole esep_head_train call (prefix sweep, training sweep, row "
-                                "finish, scalars, guarded launches); the sweep kernel is about 95 % "
-                                "of it, see profiles/launch_list_bench_c2.md"},
-        "roofline_two_kernel_path": {
-            "head_fwd_kernel": {"achieved": fwd_tf, "frac": fwd_tf / peaks["tflops"], "ms": ms_fwd,
-                                "traffic": _traffic("head_fwd_kernel")},
-            "head_bwd_kernel": {"achieved": bwd_tf, "frac": bwd_tf / peaks["tflops"], "ms": ms_bwd,
-                                "executed_tflops": f_exec_bwd / (ms_bwd * 1e-3) / 1e12,
-                                "traffic": _traffic("head_bwd_kernel")},
-            "note": "used without gradient, for batches with many ignored rows, for vocabulary "
-                    "shards and as the guarded second attempt of the single sweep"},
-        "step_tensor_frac": (f_alg_fwd + f_alg_bwd) / (ms_step * 1e-3) / 1e12 / peaks["tflops"],
+                              "once); the single pass executes 4*H*V*N",
+                     "ms": ms_call,
+                     "ms_note": "mean over the timed steps of the CUDA-event time of the whole "
+                                "esep_head_step call inside the timed loop (row classes, gather, "
+                                "prefix sweep, training sweep, row finish, scalars, guarded launches); "
+                                "the training sweep is about 95 % of it (profiles/)"},
+        "step_tensor_frac": f_alg / (ms_step * 1e-3) / 1e12 / peaks["tflops"],
         "device_status": status,
         "plan": {"sm_count": caps.sm_count, "bwd_clusters_resident": caps.max_clusters_bwd,
-                 "fwd_splits": pl.fwd_splits, "fwd_grid": pl.fwd_grid, "bwd_full_rounds": pl.bwd_full_rounds, "bwd_rem_pairs": pl.bwd_rem_pairs,
-                 "bwd_rem_splits": pl.bwd_rem_splits,
-                 "bwd_grid": pl.bwd_grid},
+                 "row_tiles": pl.fwd_row_tiles, "sweep_full_rounds": pl.bwd_full_rounds,
+                 "sweep_left_over_tiles": pl.bwd_rem_pairs, "sweep_runs": pl.bwd_rem_splits,
+                 "sweep_grid": pl.bwd_grid},
     }
+    line.update(line_extra)
     if world == 1:
-        rate, rows, dt = cpu_reference_rate(cfg)
-        line["cpu_baseline"] = {"value": rate, "unit": UNIT, "cores": torch.get_num_threads(),
-                                "kind": "port",
-                                "sample": f"{rows} rows (passes over the first rows of the {n}-row "
-                                          f"batch), fwd+dX, {dt:.1f} s"}
+        line["cpu_baseline"] = cpu_baseline_block(cfg)
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def _timed_ranks(dist, dev, fn, steps, warm):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    return ms.item() / steps
+
+
+def _strong_c3(dist, par, make_config, dev, rank, world, peaks, args):
+    """16 384 bf16 rows split evenly over the ranks (W replicated, one 8-scalar all-reduce)."""
+    cfg = make_config("c3", seed=0)                 # the same rows on every rank: each takes its slice
+    meta = cfg["meta"]
+    n, h, v = meta["n"], meta["h"], meta["v"]
+    lo, hi = par.shard_bounds(n, world, rank)
+    w = cfg["w"].to(dev)
+    xs, ts, cs = cfg["x"][lo:hi].to(dev), cfg["target"][lo:hi].to(dev), cfg["ce_weight"][lo:hi].to(dev)
+    steps = max(3, min(args.steps, 10))
+
+    def step():
+        return par.token_sharded_linear_ce(xs, w, ts, cs)
+
+    ms = _timed_ranks(dist, dev, step, steps, 3)
+    # the same 16 384 rows on ONE GPU (every rank does it; the slowest counts)
+    xa, ta, ca = cfg["x"].to(dev), cfg["target"].to(dev), cfg["ce_weight"].to(dev)
+    ms1 = _timed_ranks(dist, dev, lambda: _single(xa, w, ta, ca), 3, 2)
+    del xa, ta, ca
+    loss, stats, dx, metrics = step()
+    out = {"rows_total": n, "rows_per_gpu": hi - lo, "dtype": meta["dtype"], "steps": steps,
+           "ms_per_step": ms, "tokens_s": n / (ms * 1e-3), "ms_per_step_1gpu_same_rows": ms1,
+           "efficiency_vs_1gpu_same_rows": ms1 / (world * ms),
+           "step_tensor_frac": 4.0 * h * v * (hi - lo) / (ms * 1e-3) / 1e12 / peaks["tflops"],
+           "metrics_all_ranks": [float(m) for m in metrics[:4].tolist()]}
+    if rank == 0:
+        rows = torch.arange(0, hi - lo, max(1, (hi - lo) // 64))[:64]
+        out["parity"] = _parity(cfg["x"][lo:hi], cfg["w"], cfg["target"][lo:hi],
+                                cfg["ce_weight"][lo:hi], (stats["ce"] * cs).float().cpu(), stats,
+                                dx, rows)
+    return out
+
+
+def _single(x, w, t, c):
+    """The token-sharded call without its all-reduce (one GPU's view of the whole batch)."""
+    from esep_soup_kernels_b200.head import op as head_op
+
+    return head_op._run_step(x, w, True, target=t, ce_weight=c)
+
+
+def _vocab_parallel_c4(dist, par, make_config, make_weight, shape, dev, rank, world, peaks, args):
+    """32 768 x 3584 bf16 rows against a 152 064-row W split by vocabulary rows over the ranks."""
+    n, h, v = 32768, shape["h"], shape["v"]
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(n, h, generator=g).to(torch.bfloat16)
+    target = torch.randint(0, v, (n,), generator=g)
+    target[torch.rand(n, generator=g) < 0.05] = -100
+    cew = (target >= 0).float()
+    lo, hi = par.shard_bounds(v, world, rank)
+    # W = the concatenation of `world` independently seeded shards
+    w_shard = make_weight(hi - lo, h, shape["w_std"], torch.bfloat16, seed=100 + rank).to(dev)
+    xd, td, cd = x.to(dev), target.to(dev), cew.to(dev)
+    steps = max(3, min(args.steps, 6))
+    timings = []
+
+    def step(tm=None):
+        return par.vocab_parallel_linear_ce(xd, w_shard, td, cd, lo, v, timings=tm)
+
+    ms = _timed_ranks(dist, dev, step, steps, 2)
+    loss, stats, dx = step(timings)
+    torch.cuda.synchronize()
+    marks = dict(timings)
+    split = {k: marks[a].elapsed_time(marks[b]) for k, a, b in (
+        ("sweep_ms", "start", "sweep"), ("exchange_ms", "sweep", "exchange"),
+        ("combine_ms", "exchange", "combine"), ("dx_allreduce_ms", "combine", "reduce"))}
+    n_live = int((target >= 0).sum())
+    f_alg_gpu = (2.0 * h * (hi - lo) * n + 2.0 * h * (hi - lo) * n_live)
+    # every rank must hold the same dHidden bits after the all-reduce
+    chk = torch.stack([dx.double().sum(), dx[::97].double().abs().sum()])
+    lo_chk, hi_chk = chk.clone(), chk.clone()
+    dist.all_reduce(lo_chk, op=dist.ReduceOp.MIN)
+    dist.all_reduce(hi_chk, op=dist.ReduceOp.MAX)
+    out = {"rows": n, "hidden": h, "vocab": v, "shards": world, "vocab_rows_per_gpu": hi - lo,
+           "dtype": "bfloat16", "steps": steps, "ms_per_step": ms, "tokens_s": n / (ms * 1e-3),
+           "tensor_frac": f_alg_gpu / (ms * 1e-3) / 1e12 / peaks["tflops"],
+           "time_split_rank0": split, "dx_identical_on_all_ranks": bool((lo_chk == hi_chk).all()),
+           "note": "the 7B hidden size needs three passes over the hidden dimension per row tile "
+                   "(4 CTAs x 384 accumulator columns = 1536 of 3584), each recomputing the logits"}
+    # parity: the oracle needs the whole W on the host; rank 0 rebuilds the other shards
+    sub = torch.arange(0, n, n // 64)[:64]
+    if rank == 0:
+        shards = [make_weight(par.shard_bounds(v, world, r)[1] - par.shard_bounds(v, world, r)[0], h,
+                              shape["w_std"], torch.bfloat16, seed=100 + r) for r in range(world)]
+        w_full = torch.cat(shards)
+        out["parity"] = _parity(x, w_full, target, cew, (stats["ce"] * cd).float().cpu(), stats, dx,
+                                sub)
+    return out
 
 
 def main():
@@ -376,10 +573,11 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", default="c2")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
+        if args.steps > 20:      # a pass over the batch takes seconds on the host
+            args.steps = 20
         run_reference(args)
     else:
         run_ours(args)

@@ -40,6 +40,7 @@ std::atomic<int> g_ready[kMaxDevices];
 DeviceInfo g_info[kMaxDevices];
 PFN_cuTensorMapEncodeTiled g_encode = nullptr;
 std::atomic<long long> g_init_calls{0};   // completed per-device initialisations (test aid)
+std::atomic<long long> g_launches{0};     // kernels this library has launched (all entry points)
 
 size_t align_up(size_t x) { return (x + kAlign - 1) / kAlign * kAlign; }
 
@@ -470,6 +471,7 @@ int esep_head_forward_partial(const void* x, const void* w, const int64_t* targe
       cudaGetLastError();
       return ESEP_ERR_CUDA;
     }
+    g_launches.fetch_add(1);
   }
 
   const int threads = 256;
@@ -477,6 +479,7 @@ int esep_head_forward_partial(const void* x, const void* w, const int64_t* targe
                                                            p.ptz, p.pidx, vocab_offset, record,
                                                            g_gate);
   if (cudaGetLastError() != cudaSuccess) return ESEP_ERR_CUDA;
+  g_launches.fetch_add(1);
   return ESEP_OK;
 }
 
@@ -503,11 +506,13 @@ int esep_head_finalize(const float* records, int n_records, const int64_t* targe
       reinterpret_cast<const long long*>(target), ce_weight, lse, target_logit, ce, entropy,
       reinterpret_cast<long long*>(argmax), cew_out, g_gate);
   if (cudaGetLastError() != cudaSuccess) return ESEP_ERR_CUDA;
+  g_launches.fetch_add(1);
   head_scalars_kernel<<<1, 1024, 0, s>>>(static_cast<int>(n), v_global, ce, cew_out, entropy,
                                          reinterpret_cast<const long long*>(argmax),
                                          reinterpret_cast<const long long*>(target), status, loss,
                                          metrics, g_gate);
   if (cudaGetLastError() != cudaSuccess) return ESEP_ERR_CUDA;
+  g_launches.fetch_add(1);
   return ESEP_OK;
 }
 
@@ -608,11 +613,13 @@ int esep_head_backward(const void* x, const void* w, const int64_t* target, cons
     cudaGetLastError();
     return ESEP_ERR_CUDA;
   }
+  g_launches.fetch_add(1);
   if (pl.bwd_rem_pairs > 0) {
     head_dx_sum_kernel<<<pl.bwd_rem_pairs * 128, 128, 0, s>>>(
         p.n, p.h, pl.fwd_row_tiles, pl.bwd_full_rounds * (pl.bwd_grid / kBwdCluster),
         pl.bwd_rem_pairs, pl.bwd_rem_splits, kBwdCluster * pl.bwd_hslice, p.dx_part, dx, g_gate);
     if (cudaGetLastError() != cudaSuccess) return ESEP_ERR_CUDA;
+  g_launches.fetch_add(1);
   }
   return ESEP_OK;
 }
@@ -630,7 +637,9 @@ int esep_head_selftest_bounded_wait(void* workspace, size_t workspace_bytes, int
   int* status = static_cast<int*>(workspace);
   if (cudaMemsetAsync(status, 0, sizeof(int), s) != cudaSuccess) return ESEP_ERR_CUDA;
   head_wait_probe_kernel<<<1, 32, 0, s>>>(status, limit_cycles);
-  return cudaGetLastError() == cudaSuccess ? ESEP_OK : ESEP_ERR_CUDA;
+  if (cudaGetLastError() != cudaSuccess) return ESEP_ERR_CUDA;
+  g_launches.fetch_add(1);
+  return ESEP_OK;
 }
 
 int esep_head_device_status(const void* workspace, void* stream, int* out_status) {
@@ -764,7 +773,9 @@ int esep_head_norm_forward(const float* r_in, const void* delta, const float* ga
   ESEP_NORM_SHAPE(h / 4, ESEP_NORM_FWD_V)
 #undef ESEP_NORM_FWD_V
 #undef ESEP_NORM_FWD
-  return cudaGetLastError() == cudaSuccess ? ESEP_OK : ESEP_ERR_CUDA;
+  if (cudaGetLastError() != cudaSuccess) return ESEP_ERR_CUDA;
+  g_launches.fetch_add(1);
+  return ESEP_OK;
 }
 
 int esep_head_norm_backward(const float* dy, const float* r_out, const float* rstd,
@@ -798,7 +809,9 @@ int esep_head_norm_backward(const float* dy, const float* r_out, const float* rs
   ESEP_NORM_SHAPE(h / 4, ESEP_NORM_BWD_V)
 #undef ESEP_NORM_BWD_V
 #undef ESEP_NORM_BWD
-  return cudaGetLastError() == cudaSuccess ? ESEP_OK : ESEP_ERR_CUDA;
+  if (cudaGetLastError() != cudaSuccess) return ESEP_ERR_CUDA;
+  g_launches.fetch_add(1);
+  return ESEP_OK;
 }
 
 }  // extern "C"
@@ -889,7 +902,7 @@ struct StepArgs {
   const int64_t* attention_mask;
   int64_t seq_len;
   int need_grad;
-  float *lse, *target_logit, *ce, *entropy, *cew_out, *loss, *metrics, *dx;
+  float *lse, *target_logit, *ce, *entropy, *cew_out, *loss, *metrics, *dx, *top_logit;
   int64_t* argmax;
   int* overflow;             // may be null
   void* workspace;
@@ -916,6 +929,7 @@ int launch_cluster(K kernel, unsigned grid, unsigned block, size_t smem, unsigne
     cudaGetLastError();
     return ESEP_ERR_CUDA;
   }
+  g_launches.fetch_add(1);
   return ESEP_OK;
 }
 
@@ -981,6 +995,7 @@ int step_impl(const StepArgs& a) {
   q.status = status;
   head_step_prep_kernel<<<1, 1024, 0, s>>>(q);
   if (cudaGetLastError() != cudaSuccess) return ESEP_ERR_CUDA;
+  g_launches.fetch_add(1);
 
   // 2. compact 16-bit copy of the selected rows
   {
@@ -994,6 +1009,7 @@ int step_impl(const StepArgs& a) {
       else head_step_gather_kernel<1, false><<<grid, 128, 0, s>>>(a.x, perm, h, xc);
     }
     if (cudaGetLastError() != cudaSuccess) return ESEP_ERR_CUDA;
+  g_launches.fetch_add(1);
   }
 
   const size_t st_stride = t.st_stride, lo_stride = t.lo_stride;
@@ -1129,20 +1145,24 @@ int step_impl(const StepArgs& a) {
   r.pm = f.pm; r.ps = f.ps; r.pt = f.pt; r.ptz = f.ptz; r.pidx = f.pidx;
   r.f_lse = fb; r.f_tl = fb + fbs; r.f_ce = fb + 2 * fbs; r.f_ent = fb + 3 * fbs;
   r.f_cew = fb + 4 * fbs;
+  r.f_max = reinterpret_cast<const float*>(ws + pl.ws_record_off);   // esep_head_forward's record
   r.f_amax = fb_amax;
   r.lse = a.lse; r.tlogit = a.target_logit; r.ce = a.ce; r.ent = a.entropy; r.cew_out = a.cew_out;
   r.amax = reinterpret_cast<long long*>(a.argmax);
+  r.top = a.top_logit;
   r.dx = need_grad ? a.dx : nullptr;
   if (a.dtype == ESEP_DTYPE_F16)
     head_step_rows_kernel<0><<<static_cast<unsigned>(m), 128, 0, s>>>(r);
   else
     head_step_rows_kernel<1><<<static_cast<unsigned>(m), 128, 0, s>>>(r);
   if (cudaGetLastError() != cudaSuccess) return ESEP_ERR_CUDA;
+  g_launches.fetch_add(1);
   head_step_scalars_kernel<<<1, 1024, 0, s>>>(m, a.v, a.ce, a.cew_out, a.entropy,
                                               reinterpret_cast<const long long*>(a.argmax), tgt_o,
                                               step_mode ? q.attn : nullptr, counts, status, a.loss,
                                               a.metrics);
   if (cudaGetLastError() != cudaSuccess) return ESEP_ERR_CUDA;
+  g_launches.fetch_add(1);
   return ESEP_OK;
 }
 }  // namespace
@@ -1164,14 +1184,16 @@ int esep_head_step(const void* x, int x_dtype, const void* w, const void* w_bf16
                    const int64_t* labels, const int64_t* attention_mask, int64_t seq_len,
                    int need_grad, float* lse, float* target_logit, float* ce, float* entropy,
                    int64_t* argmax, float* cew_out, float* loss, float* metrics, float* dx,
-                   int* overflow, void* workspace, size_t workspace_bytes, void* stream) {
+                   float* top_logit, int* overflow, void* workspace, size_t workspace_bytes,
+                   void* stream) {
   StepArgs a = {};
   a.x = x; a.x_dtype = x_dtype; a.w = w; a.w_bf16 = w_bf16; a.dtype = dtype;
   a.m = m; a.h = h; a.v = v;
   a.target = target; a.ce_weight = ce_weight; a.labels = labels;
   a.attention_mask = attention_mask; a.seq_len = seq_len; a.need_grad = need_grad;
   a.lse = lse; a.target_logit = target_logit; a.ce = ce; a.entropy = entropy; a.argmax = argmax;
-  a.cew_out = cew_out; a.loss = loss; a.metrics = metrics; a.dx = dx; a.overflow = overflow;
+  a.cew_out = cew_out; a.loss = loss; a.metrics = metrics; a.dx = dx; a.top_logit = top_logit;
+  a.overflow = overflow;
   a.workspace = workspace; a.workspace_bytes = workspace_bytes; a.stream = stream;
   return step_impl(a);
 }
@@ -1194,7 +1216,7 @@ int esep_head_train(const void* x, const void* w, const void* w_bf16, const int6
   }
   const int st = esep_head_step(x, dtype, w, w_bf16, dtype, n, h, v, target, ce_weight, nullptr,
                                 nullptr, 0, 1, lse, target_logit, ce, entropy, argmax, cew_out, loss,
-                                m8, dx, overflow, workspace, workspace_bytes, stream);
+                                m8, dx, nullptr, overflow, workspace, workspace_bytes, stream);
   if (st != ESEP_OK || metrics == nullptr) return st;
   return cudaMemcpyAsync(metrics, m8, ESEP_METRIC_SCALARS * sizeof(float),
                          cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream)) == cudaSuccess
@@ -1202,10 +1224,92 @@ int esep_head_train(const void* x, const void* w, const void* w_bf16, const int6
              : ESEP_ERR_CUDA;
 }
 
+int esep_head_vp_prepare(const int64_t* target, int64_t n, int64_t vocab_offset, int64_t v_local,
+                         int64_t v_global, int64_t* local_target, float* unit_weight,
+                         void* stream) {
+  if (target == nullptr || local_target == nullptr || unit_weight == nullptr || n <= 0 ||
+      n > (1 << 30) || v_local <= 0 || v_global <= 0 || vocab_offset < 0)
+    return ESEP_ERR_BAD_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  head_vp_prepare_kernel<<<div_up(n, 256), 256, 0, s>>>(
+      static_cast<int>(n), v_global, vocab_offset, v_local,
+      reinterpret_cast<const long long*>(target), reinterpret_cast<long long*>(local_target),
+      unit_weight);
+  if (cudaGetLastError() != cudaSuccess) return ESEP_ERR_CUDA;
+  g_launches.fetch_add(1);
+  return ESEP_OK;
+}
+
+int esep_head_vp_pack(const float* lse, const float* entropy, const float* top_logit,
+                      const float* target_logit, const int64_t* argmax_local,
+                      const int64_t* target, int64_t n, int64_t vocab_offset, int64_t v_local,
+                      int64_t v_global, float* record, void* stream) {
+  if (lse == nullptr || entropy == nullptr || top_logit == nullptr || target_logit == nullptr ||
+      argmax_local == nullptr || target == nullptr || record == nullptr || n <= 0 ||
+      n > (1 << 30))
+    return ESEP_ERR_BAD_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  head_vp_pack_kernel<<<div_up(n, 256), 256, 0, s>>>(
+      static_cast<int>(n), v_global, vocab_offset, v_local,
+      reinterpret_cast<const long long*>(target), lse, entropy, top_logit, target_logit,
+      reinterpret_cast<const long long*>(argmax_local), record);
+  if (cudaGetLastError() != cudaSuccess) return ESEP_ERR_CUDA;
+  g_launches.fetch_add(1);
+  return ESEP_OK;
+}
+
+int esep_head_vp_combine(const float* records, int n_records, int my_record,
+                         const int64_t* target, const float* ce_weight, const void* w_shard,
+                         int64_t n, int64_t h, int64_t v_local, int64_t vocab_offset,
+                         int64_t v_global, int dtype, float* dx, float* lse, float* target_logit,
+                         float* ce, float* entropy, int64_t* argmax, float* cew_out, float* loss,
+                         float* metrics, void* stream) {
+  if (records == nullptr || target == nullptr || ce_weight == nullptr || w_shard == nullptr ||
+      dx == nullptr || lse == nullptr || target_logit == nullptr || ce == nullptr ||
+      entropy == nullptr || argmax == nullptr || cew_out == nullptr || loss == nullptr)
+    return ESEP_ERR_BAD_ARG;
+  if (n <= 0 || n > (1 << 30) || h <= 0 || h % 8 != 0 || v_local <= 0 || v_global <= 0 ||
+      n_records <= 0 || my_record < 0 || my_record >= n_records)
+    return ESEP_ERR_BAD_ARG;
+  if (dtype != ESEP_DTYPE_F16 && dtype != ESEP_DTYPE_BF16) return ESEP_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(dx) & 15u) || (reinterpret_cast<uintptr_t>(w_shard) & 15u))
+    return ESEP_ERR_ALIGNMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  VpCombineParams q = {};
+  q.n = static_cast<int>(n);
+  q.h = static_cast<int>(h);
+  q.k_parts = n_records;
+  q.me = my_record;
+  q.v_global = v_global;
+  q.vocab_offset = vocab_offset;
+  q.v_local = v_local;
+  q.records = records;
+  q.target = reinterpret_cast<const long long*>(target);
+  q.ce_weight = ce_weight;
+  q.w_shard = w_shard;
+  q.dx = dx;
+  q.lse = lse; q.tlogit = target_logit; q.ce = ce; q.ent = entropy; q.cew_out = cew_out;
+  q.amax = reinterpret_cast<long long*>(argmax);
+  if (dtype == ESEP_DTYPE_F16)
+    head_vp_combine_kernel<0><<<static_cast<unsigned>(n), 128, 0, s>>>(q);
+  else
+    head_vp_combine_kernel<1><<<static_cast<unsigned>(n), 128, 0, s>>>(q);
+  if (cudaGetLastError() != cudaSuccess) return ESEP_ERR_CUDA;
+  g_launches.fetch_add(1);
+  head_scalars_kernel<<<1, 1024, 0, s>>>(q.n, v_global, ce, cew_out, entropy,
+                                         reinterpret_cast<const long long*>(argmax),
+                                         reinterpret_cast<const long long*>(target), nullptr, loss,
+                                         metrics);
+  if (cudaGetLastError() != cudaSuccess) return ESEP_ERR_CUDA;
+  g_launches.fetch_add(1);
+  return ESEP_OK;
+}
+
 int esep_head_debug_counters(long long* out, int n) {
   if (out == nullptr || n < 2) return ESEP_ERR_BAD_ARG;
   out[0] = g_init_calls.load();
   out[1] = g_tmap_encodes.load();
+  if (n >= 3) out[2] = g_launches.load();
   return ESEP_OK;
 }
 

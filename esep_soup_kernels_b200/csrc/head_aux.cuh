@@ -2,6 +2,9 @@
 // per-row outputs, the scalar loss / metric reduction and the sum of partial dHidden buffers.
 #pragma once
 
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
 #include "head_fwd.cuh"
 
 namespace esep {
@@ -166,6 +169,135 @@ __global__ void head_dx_sum_kernel(int n, int h, int n_row_tiles, int first_tp, 
       a.w += b.w;
     }
     *reinterpret_cast<float4*>(dx + static_cast<size_t>(row) * h + col0 + cidx) = a;
+  }
+}
+
+// ---- vocabulary shards that each ran the single pass as a vocabulary of their own ----------------
+// Every shard k sweeps its rows of W with a LOCAL softmax: local lse_k, local entropy H_k, its
+// largest logit and where it sits, the target logit on the shard that owns the target, and
+// dX_k = p_k W_k - W_k[t_k] for a local target t_k with unit weight. The global results follow
+// from one exchange of five numbers per row and shard:
+//     lse = logsumexp_k lse_k        a_k = e^(lse_k - lse)      (softmax = a_k p_k on shard k)
+//     entropy = lse - sum_k a_k (lse_k - H_k)
+//     argmax: the shard whose largest logit is largest, lowest global index on equal values
+//     dX = cew (sum_k a_k p_k W_k - W[target])
+// Rows whose target lives on another shard sweep with local target 0 as a stand-in and the row
+// W_k[0] is added back; on the owner the two target terms combine to -(1 - a_k) W[target], with
+// 1 - a_k formed from the OTHER shards' a so that a confident row loses nothing to cancellation.
+
+// Local target and unit weight of every row for the shard [vocab_offset, vocab_offset + v_local).
+__global__ void head_vp_prepare_kernel(int n, long long v_global, long long vocab_offset,
+                                       long long v_local, const long long* __restrict__ target,
+                                       long long* __restrict__ local_target,
+                                       float* __restrict__ unit_weight) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= n) return;
+  const long long tg = target[row];
+  const bool valid = tg >= 0 && tg < v_global;
+  const long long tl = tg - vocab_offset;
+  const bool owner = valid && tl >= 0 && tl < v_local;
+  local_target[row] = owner ? tl : (valid ? 0 : -100);
+  unit_weight[row] = valid ? 1.f : 0.f;
+}
+
+// The record a shard sends: [5][n] = lse_k, H_k, largest logit, target logit (owner only, else
+// 0), global index of the largest logit (an int32 stored bit for bit).
+__global__ void head_vp_pack_kernel(int n, long long v_global, long long vocab_offset,
+                                    long long v_local, const long long* __restrict__ target,
+                                    const float* __restrict__ lse, const float* __restrict__ ent,
+                                    const float* __restrict__ top,
+                                    const float* __restrict__ tlogit,
+                                    const long long* __restrict__ amax_local,
+                                    float* __restrict__ record) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= n) return;
+  const long long tg = target[row];
+  const long long tl = tg - vocab_offset;
+  const bool owner = tg >= 0 && tg < v_global && tl >= 0 && tl < v_local;
+  const size_t ns = static_cast<size_t>(n);
+  record[row] = lse[row];
+  record[ns + row] = ent[row];
+  record[2 * ns + row] = top[row];
+  record[3 * ns + row] = owner ? tlogit[row] : 0.f;
+  record[4 * ns + row] = __int_as_float(static_cast<int>(amax_local[row] + vocab_offset));
+}
+
+struct VpCombineParams {
+  int n, h, k_parts, me;
+  long long v_global, vocab_offset, v_local;
+  const float* records;        // [k_parts][5][n], shard order
+  const long long* target;     // [n] global ids
+  const float* ce_weight;      // [n]
+  const void* w_shard;         // [v_local, h]
+  float* dx;                   // [n, h] in: the local sweep's dX_k (unit weight); out: this shard's
+                               // share of dHidden
+  float *lse, *tlogit, *ce, *ent, *cew_out;
+  long long* amax;
+};
+
+// One block of 128 threads per row; every thread forms the row's scalars itself (k_parts is
+// small), then the block rewrites the row of dx in place.
+template <int kFmt>
+__global__ void __launch_bounds__(128) head_vp_combine_kernel(const VpCombineParams q) {
+  const int row = blockIdx.x;
+  const size_t ns = static_cast<size_t>(q.n);
+  const size_t stride = 5 * ns;
+  float big = NEG_BIG;
+  for (int k = 0; k < q.k_parts; ++k) big = fmaxf(big, q.records[k * stride + row]);
+  float se = 0.f;
+  for (int k = 0; k < q.k_parts; ++k) se += __expf(q.records[k * stride + row] - big);
+  const float lse = big + logf(se);
+  float mix = 0.f, tz = 0.f, best = -INFINITY, a_me = 0.f, a_rest = 0.f;
+  int idx = 0x7fffffff;
+  for (int k = 0; k < q.k_parts; ++k) {
+    const float* r = q.records + k * stride;
+    const float lk = r[row];
+    const float ak = __expf(lk - lse);
+    mix += ak * (lk - r[ns + row]);
+    tz += r[3 * ns + row];
+    const float tk = r[2 * ns + row];
+    const int ik = __float_as_int(r[4 * ns + row]);
+    if (tk > best || (tk == best && ik < idx)) {
+      best = tk;
+      idx = ik;
+    }
+    if (k == q.me) a_me = ak; else a_rest += ak;
+  }
+  const long long tg = q.target[row];
+  const bool valid = tg >= 0 && tg < q.v_global;
+  const float cw = valid ? q.ce_weight[row] : 0.f;
+  if (threadIdx.x == 0) {
+    q.lse[row] = lse;
+    q.ent[row] = lse - mix;
+    q.amax[row] = idx;
+    q.tlogit[row] = valid ? tz : 0.f;
+    q.ce[row] = valid ? (lse - tz) : 0.f;
+    q.cew_out[row] = cw;
+  }
+  const long long tl = tg - q.vocab_offset;
+  const bool owner = valid && tl >= 0 && tl < q.v_local;
+  // a p_k W_k - a W_k[t_k] + coef W_k[t_k]: coef = a on a stand-in target (adds the row back),
+  // -(1 - a) on the owner (the rest of the -W[target] term)
+  const float coef = owner ? -a_rest : a_me;
+  const size_t wrow = static_cast<size_t>(owner ? tl : 0) * q.h;
+  float* drow = q.dx + static_cast<size_t>(row) * q.h;
+  for (int c = threadIdx.x * 4; c < q.h; c += 128 * 4) {
+    float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (cw != 0.f) {
+      const float4 d = *reinterpret_cast<const float4*>(drow + c);
+      const uint2 raw = reinterpret_cast<const uint2*>(q.w_shard)[(wrow + c) / 4];
+      float2 w01, w23;
+      if (kFmt == 0) {
+        w01 = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+        w23 = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+      } else {
+        w01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+        w23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+      }
+      val = make_float4(cw * (a_me * d.x + coef * w01.x), cw * (a_me * d.y + coef * w01.y),
+                        cw * (a_me * d.z + coef * w23.x), cw * (a_me * d.w + coef * w23.y));
+    }
+    *reinterpret_cast<float4*>(drow + c) = val;
   }
 }
 

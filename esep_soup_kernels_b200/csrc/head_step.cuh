@@ -208,9 +208,11 @@ struct StepRowsParams {
   const float *pm, *ps, *pt, *ptz;        // forward partial records [split][row - n_sweep]
   const int* pidx;
   const float *f_lse, *f_tl, *f_ce, *f_ent, *f_cew;   // compact outputs of the guarded pass
+  const float* f_max;                     // its merged record, field 0: the row maximum
   const long long* f_amax;
   float *lse, *tlogit, *ce, *ent, *cew_out;
   long long* amax;
+  float* top;                             // null, or [m]: the largest logit of every selected row
   float* dx;                              // [m, h] or null (no gradient wanted)
 };
 
@@ -223,7 +225,7 @@ __global__ void __launch_bounds__(128) head_step_rows_kernel(const StepRowsParam
   const int pos = q.inv[r];
   const int n_sweep = q.counts[CNT_SWEEP];
   float* drow = q.dx != nullptr ? q.dx + static_cast<size_t>(r) * q.h : nullptr;
-  float o_lse = 0.f, o_tl = 0.f, o_ce = 0.f, o_ent = 0.f, o_cw = 0.f;
+  float o_lse = 0.f, o_tl = 0.f, o_ce = 0.f, o_ent = 0.f, o_cw = 0.f, o_top = 0.f;
   long long o_am = 0;
   enum { DX_ZERO, DX_COPY, DX_FINISH } dx_mode = DX_ZERO;
   float inv_s = 0.f, coef = 0.f;          // DX_FINISH: dx = cw (raw * inv_s - coef * W[target])
@@ -236,6 +238,7 @@ __global__ void __launch_bounds__(128) head_step_rows_kernel(const StepRowsParam
     o_ent = q.f_ent[pos];
     o_cw = q.f_cew[pos];
     o_am = q.f_amax[pos];
+    o_top = q.f_max[pos];
     dx_mode = DX_COPY;
   } else if (pos >= 0 && pos < n_sweep) {
     // ---- sweep row: partial statistics, all relative to m_ref ---------------------------------
@@ -334,6 +337,7 @@ __global__ void __launch_bounds__(128) head_step_rows_kernel(const StepRowsParam
     o_lse = m + log_s;
     o_ent = log_s - t / s;
     o_am = idx;
+    o_top = mx;
     o_tl = valid ? tz : 0.f;
     // ln s - (z_t - m) = ln(1 + s_rest / p_t): the form without cancellation for confident rows
     o_ce = valid ? (s_rest < p_t ? log1pf(s_rest / p_t) : (o_lse - tz)) : 0.f;
@@ -420,6 +424,7 @@ __global__ void __launch_bounds__(128) head_step_rows_kernel(const StepRowsParam
     o_lse = big + log_s;
     o_ent = log_s - t / s;
     o_am = idx;
+    o_top = big;
     o_tl = valid ? tz : 0.f;
     o_ce = valid ? (o_lse - tz) : 0.f;
     o_cw = q.cew_c[pos];
@@ -432,6 +437,7 @@ __global__ void __launch_bounds__(128) head_step_rows_kernel(const StepRowsParam
     q.ent[r] = o_ent;
     q.amax[r] = o_am;
     q.cew_out[r] = o_cw;
+    if (q.top != nullptr) q.top[r] = o_top;
   }
   if (drow != nullptr && dx_mode != DX_FINISH) {
     const float* src = dx_mode == DX_COPY ? q.dxc + static_cast<size_t>(pos) * q.h : nullptr;

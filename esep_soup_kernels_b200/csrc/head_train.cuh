@@ -30,7 +30,8 @@
 //     same butterfly with fmaxf on the exact fp32 logits, and only when some row of the chunk
 //     beats its running maximum (strictly: an earlier, i.e. lower, vocabulary index keeps equal
 //     values) a second pass finds the lowest lane that holds that maximum (kernels.py:60, 75:
-//     first index of the max). P is packed and handed to G2 first, the sums follow;
+//     first index of the max). Every exponential is computed once and feeds both the row sums
+//     and the packed P;
 //   * the accumulator is drained raw; the -onehot term and all scaling moved to the row kernel;
 //   * the row's TARGET entry is left out of P and of the sums: for a confident row p_target / s is
 //     1 - tiny, and forming it from a bf16-rounded p would lose the tiny part. The row kernel adds
@@ -504,7 +505,7 @@ head_train_kernel(const __grid_constant__ CUtensorMap tmap_x,    // x [n, h], bo
         e[2] = (!v_ok || tg4.z == my_v) ? 0.f : ex2_approx(a[2]);
         e[3] = (!v_ok || tg4.w == my_v) ? 0.f : ex2_approx(a[3]);
       };
-      // First half of a step's work: the packed bf16 P that G2 is waiting for.
+      // The packed bf16 P alone (passes over the hidden dimension that do not own the statistics).
       auto chunk_pack = [&](const uint32_t (&z)[32], int ch, bool v_ok, int vbase) {
         const float* c2p = row_c2 + hf * 64 + ch * 32;
         const int* tgp = row_tg + hf * 64 + ch * 32;
@@ -517,7 +518,7 @@ head_train_kernel(const __grid_constant__ CUtensorMap tmap_x,    // x [n, h], bo
           pk[ch * 16 + j / 2 + 1] = pack2<1>(e[2], e[3]);
         }
       };
-      // Second half: row maxima and the row sums s = sum p, t = sum p (z - m_ref). Destroys z.
+      // Row maxima, the row sums s = sum p, t = sum p (z - m_ref), and the packed P. Destroys z.
       auto chunk_stats = [&](uint32_t (&z)[32], int ch, bool v_ok, int vbase) {
         const float* c2p = row_c2 + hf * 64 + ch * 32;
         const int* tgp = row_tg + hf * 64 + ch * 32;
@@ -567,6 +568,8 @@ head_train_kernel(const __grid_constant__ CUtensorMap tmap_x,    // x [n, h], bo
             // q = p * (z - m_ref) in nats; the logits registers are free now
             z[j + i] = __float_as_uint(e[i] * (a[i] * LN2));
           }
+          pk[ch * 16 + j / 2 + 0] = pack2<1>(e[0], e[1]);
+          pk[ch * 16 + j / 2 + 1] = pack2<1>(e[2], e[3]);
         }
         s_run[ch] += warp_transpose_sum(tmp, lane);
 #pragma unroll
@@ -603,17 +606,17 @@ head_train_kernel(const __grid_constant__ CUtensorMap tmap_x,    // x [n, h], bo
       for (int s = s0; s < s1 && ok; ++s, ++scount) {
         const int vbase = s * STEP_V + static_cast<int>(c) * BV + quad * 32;
         const bool v_ok = (vbase + lane) < p.v;
-        chunk_pack(z0, 0, v_ok, vbase);
-        chunk_pack(z1, 1, v_ok, vbase);
-        // G2 waits for P: hand it over at once if its buffer is already free, else after the sums
         bool stored = false, drained = (s + 1 >= s1);
-        if (__all_sync(0xffffffffu, mbar_test_wait_cluster(p_empty, (scount & 1u) ^ 1u))) {
-          ok = hand_over();
-          stored = true;
-          if (!ok) break;
+        // One exponential per logit: in the pass that owns the statistics the same values feed the
+        // row sums and the packed P. P of this step is not needed before the G2 stream has worked
+        // through the previous step's blocks, so forming the sums first costs it nothing.
+        if (pass == 0) {
+          chunk_stats(z0, 0, v_ok, vbase);
+          chunk_stats(z1, 1, v_ok, vbase);
+        } else {
+          chunk_pack(z0, 0, v_ok, vbase);
+          chunk_pack(z1, 1, v_ok, vbase);
         }
-        chunk_stats(z0, 0, v_ok, vbase);
-        chunk_stats(z1, 1, v_ok, vbase);
         const long long t0 = clock64();
         while (ok && !(stored && drained)) {
           if (!stored &&

@@ -100,16 +100,25 @@ class DeviceBackend:
         self.n, self.h = x16.shape
         self.v_local = w16.shape[0]
         self.dtype = _DTYPES[w16.dtype]
-        with torch.cuda.device(self.device):
-            nbytes = self.lib.esep_head_workspace_bytes(self.n, self.h, self.v_local, self.dtype,
-                                                        int(need_grad))
-        if nbytes == 0:
-            code, _ = _lib.query(self.device.index)
-            _lib.check("esep_head_query", code)
-            raise _lib.HeadLibraryError("esep_head_workspace_bytes", -1, "no plan for this size")
-        self.ws = torch.empty(nbytes, device=self.device, dtype=torch.uint8)
-        self.ws[:256].zero_()   # device status word (a backward-only call never clears it)
-        _remember(self.device, self.ws, None)
+        self.need_grad = bool(need_grad)
+        self._ws = None
+
+    @property
+    def ws(self):
+        """Workspace of the forward / backward sweeps, allocated when one of them first runs."""
+        if self._ws is None:
+            with torch.cuda.device(self.device):
+                nbytes = self.lib.esep_head_workspace_bytes(self.n, self.h, self.v_local,
+                                                            self.dtype, int(self.need_grad))
+            if nbytes == 0:
+                code, _ = _lib.query(self.device.index)
+                _lib.check("esep_head_query", code)
+                raise _lib.HeadLibraryError("esep_head_workspace_bytes", -1,
+                                            "no plan for this size")
+            self._ws = torch.empty(nbytes, device=self.device, dtype=torch.uint8)
+            self._ws[:256].zero_()   # device status word (a backward-only call never clears it)
+            _remember(self.device, self._ws, None)
+        return self._ws
 
     def forward_partial(self, x16, w16, target, vocab_offset=0):
         rec = torch.empty(_lib.RECORD_FIELDS, self.n, device=self.device, dtype=torch.float32)
@@ -142,8 +151,52 @@ class DeviceBackend:
         """Single pass over this weight as a vocabulary of its own: statistics and dHidden of
         every row. Returns the finalize() dictionary plus "dx" and "overflow" (device int: 1 if
         the guarded two-kernel path produced the outputs)."""
-        out = _run_step(x16, w16, True, target=target, ce_weight=ce_weight, w_bf16=w_bf16)
+        out = _run_step(x16, w16, True, target=target, ce_weight=ce_weight, w_bf16=w_bf16,
+                        want_top=True)
         out["metrics"] = out["metrics"][:_lib.METRIC_SCALARS]
+        return out
+
+    # ---- vocabulary shards on the single pass (formulas: csrc/head_aux.cuh) -----------------
+    def vp_prepare(self, target, vocab_offset, v_local, v_global):
+        """(local target, unit weight) of every row for this rank's shard."""
+        n, dev = self.n, self.device
+        local_target = torch.empty(n, device=dev, dtype=torch.int64)
+        unit = torch.empty(n, device=dev, dtype=torch.float32)
+        with torch.cuda.device(dev):
+            code = self.lib.esep_head_vp_prepare(_ptr(target), n, vocab_offset, v_local, v_global,
+                                                 _ptr(local_target), _ptr(unit), _stream(dev))
+        _lib.check("esep_head_vp_prepare", code)
+        return local_target, unit
+
+    def vp_pack(self, out, target, vocab_offset, v_local, v_global):
+        """This rank's [5, n] record from the outputs of its local train() call."""
+        n, dev = self.n, self.device
+        rec = torch.empty(_lib.RECORD_FIELDS, n, device=dev, dtype=torch.float32)
+        with torch.cuda.device(dev):
+            code = self.lib.esep_head_vp_pack(
+                _ptr(out["lse"]), _ptr(out["entropy"]), _ptr(out["top"]), _ptr(out["target_logit"]),
+                _ptr(out["argmax"]), _ptr(target), n, vocab_offset, v_local, v_global, _ptr(rec),
+                _stream(dev))
+        _lib.check("esep_head_vp_pack", code)
+        return rec
+
+    def vp_combine(self, records, me, target, ce_weight, w_shard, vocab_offset, v_global, dx):
+        """Global statistics from all ranks' records; dx (the local sweep's result) is rewritten
+        in place into this rank's share of dHidden."""
+        n, dev = self.n, self.device
+        f = torch.empty(5 * n + 1 + _lib.METRIC_SCALARS, device=dev, dtype=torch.float32)
+        out = {"lse": f[0:n], "target_logit": f[n:2 * n], "ce": f[2 * n:3 * n],
+               "entropy": f[3 * n:4 * n], "cew": f[4 * n:5 * n], "loss": f[5 * n:5 * n + 1],
+               "metrics": f[5 * n + 1:], "argmax": torch.empty(n, device=dev, dtype=torch.int64)}
+        records = records.contiguous()
+        with torch.cuda.device(dev):
+            code = self.lib.esep_head_vp_combine(
+                _ptr(records), records.shape[0], int(me), _ptr(target), _ptr(ce_weight),
+                _ptr(w_shard), n, self.h, w_shard.shape[0], vocab_offset, v_global, self.dtype,
+                _ptr(dx), _ptr(out["lse"]), _ptr(out["target_logit"]), _ptr(out["ce"]),
+                _ptr(out["entropy"]), _ptr(out["argmax"]), _ptr(out["cew"]), _ptr(out["loss"]),
+                _ptr(out["metrics"]), _stream(dev))
+        _lib.check("esep_head_vp_combine", code)
         return out
 
     def backward(self, x16, w16, target, cew, lse, vocab_offset=0, out=None):
@@ -227,11 +280,11 @@ def _bf16_weight(w16):
 
 
 def _run_step(x, w16, need_grad, target=None, ce_weight=None, labels=None, attention_mask=None,
-              seq_len=0, w_bf16=None):
+              seq_len=0, w_bf16=None, want_top=False):
     """One ``esep_head_step`` call. x: [m, h] contiguous in w16's dtype or fp32. Flat rows
     (target, ce_weight) or a [m / seq_len, seq_len] step (labels, attention_mask). Returns a
     dict of views: the five statistics, "cew", "loss" [1], "metrics" [8], "dx" (or None) and
-    "overflow" (device int32 [1])."""
+    "overflow" (device int32 [1]); with want_top also "top", the largest logit of every row."""
     lib = _lib.load()
     dev = x.device
     m, h = x.shape
@@ -244,10 +297,11 @@ def _run_step(x, w16, need_grad, target=None, ce_weight=None, labels=None, atten
             _lib.check("esep_head_query", code)
             raise _lib.HeadLibraryError("esep_head_step_workspace_bytes", -1, "no plan for this size")
         ws = torch.empty(nbytes, device=dev, dtype=torch.uint8)
-        f = torch.empty(5 * m + 1 + _lib.STEP_SCALARS, device=dev, dtype=torch.float32)
+        f = torch.empty(6 * m + 1 + _lib.STEP_SCALARS, device=dev, dtype=torch.float32)
         out = {"lse": f[0:m], "target_logit": f[m:2 * m], "ce": f[2 * m:3 * m],
-               "entropy": f[3 * m:4 * m], "cew": f[4 * m:5 * m], "loss": f[5 * m:5 * m + 1],
-               "metrics": f[5 * m + 1:], "argmax": torch.empty(m, device=dev, dtype=torch.int64),
+               "entropy": f[3 * m:4 * m], "cew": f[4 * m:5 * m], "top": f[5 * m:6 * m],
+               "loss": f[6 * m:6 * m + 1], "metrics": f[6 * m + 1:],
+               "argmax": torch.empty(m, device=dev, dtype=torch.int64),
                "dx": torch.empty(m, h, device=dev, dtype=torch.float32) if need_grad else None}
         overflow = ws[96:100].view(torch.int32)
         if need_grad and w_bf16 is None:
@@ -257,7 +311,8 @@ def _run_step(x, w16, need_grad, target=None, ce_weight=None, labels=None, atten
             _ptr(ce_weight), _ptr(labels), _ptr(attention_mask), int(seq_len), int(need_grad),
             _ptr(out["lse"]), _ptr(out["target_logit"]), _ptr(out["ce"]), _ptr(out["entropy"]),
             _ptr(out["argmax"]), _ptr(out["cew"]), _ptr(out["loss"]), _ptr(out["metrics"]),
-            _ptr(out["dx"]), None, _ptr(ws), ws.numel(), _stream(dev))
+            _ptr(out["dx"]), _ptr(out["top"]) if want_top else None, None, _ptr(ws), ws.numel(),
+            _stream(dev))
     _lib.check("esep_head_step", code)
     out["overflow"] = overflow
     _remember(dev, ws, overflow)

@@ -7,14 +7,17 @@ token-sharded   rows of x are split across ranks, W is replicated. Every row's l
                 dHidden depend only on that row and W, so there is NO data-path collective; the
                 ranks exchange one 4-float all-reduce {loss, n_valid, n_correct, entropy_sum}
                 (it stands for the five metric gathers of solution/head/patch.py:594-612).
-vocab-parallel  W is split by vocabulary rows, every rank holds all rows of x. Each rank sweeps
-                its shard into a per-row record (m, s, t, target logit, argmax), the records are
-                all-gathered and merged with the rule of solution/head/kernels.py:70-81, each rank
-                computes the dHidden contribution of its shard and the contributions are summed
-                with an all-reduce. With dx_chunks > 1 the backward sweep runs row group by row
-                group and the all-reduce of a finished group runs (asynchronously, on the
-                collective's own stream) while the next group is swept; the sweep leaves 16 of
-                the 148 SMs free, which is where the collective's kernels run.
+vocab-parallel  W is split by vocabulary rows, every rank holds all rows of x. With a gradient
+                every rank runs the single pass on its shard as a vocabulary of its own, the
+                ranks all-gather one [5, N] record each, a combine kernel turns the local
+                results into the rank's share of the global ones and the shares of dHidden
+                are summed with an all-reduce: the only torch calls on the way are the two
+                collectives. Without the single pass (or without gradient): forward sweep into a
+                per-row record (m, s, t, target logit, argmax), all-gather, merge with the rule
+                of solution/head/kernels.py:70-81, backward sweep per shard, all-reduce. With
+                dx_chunks > 1 that backward sweep runs row group by row group and the all-reduce
+                of a finished group runs (asynchronously, on the collective's own stream) while
+                the next group is swept.
 
 Both take a `backend_factory` so that the host logic (sharding, exchange, merge order) can be
 exercised with CPU ranks on the gloo backend in the tests; the default is the CUDA library.
@@ -42,16 +45,21 @@ def token_sharded_linear_ce(x_local, w16, target_local, ce_weight_local, need_gr
                             group=None, backend_factory=_default_backend):
     """This rank's rows through the head, plus the globally reduced metric scalars.
 
-    Returns (loss_local, stats_local, dx_local, metrics) where metrics is a 4-float tensor
-    {sum of loss over all ranks, valid rows, correct rows, sum of entropy over valid rows}.
+    Returns (loss_local, stats_local, dx_local, metrics) where metrics holds, summed over all
+    ranks, {loss, valid rows, correct rows, sum of entropy over valid rows} followed (library
+    path) by the four further scalars of a step (include/esep_head.h: ESEP_STEP_SCALARS).
     loss_local / dx_local are this rank's own (dHidden never leaves the row owner)."""
     x16, target, cew = _prepare(x_local, w16, target_local, ce_weight_local)
-    be = backend_factory(x16, w16, need_grad)
-    if need_grad and op.SINGLE_SWEEP and hasattr(be, "train"):
-        # statistics and dHidden from one pass over the vocabulary (the whole W is local)
+    be = None if backend_factory is _default_backend else backend_factory(x16, w16, need_grad)
+    if be is None and (op.SINGLE_SWEEP or not need_grad):
+        # one library call for this rank's rows (the whole W is local); eight scalars
+        out = op._run_step(x16, w16, need_grad, target=target, ce_weight=cew)
+        dx = out["dx"]
+    elif be is not None and need_grad and op.SINGLE_SWEEP and hasattr(be, "train"):
         out = be.train(x16, w16, op._bf16_weight(w16), target, cew)
         dx = out["dx"]
     else:
+        be = be if be is not None else backend_factory(x16, w16, need_grad)
         rec = be.forward_partial(x16, w16, target, 0)
         out = be.finalize(rec, target, cew, w16.shape[0])
         dx = be.backward(x16, w16, target, out["cew"], out["lse"], 0) if need_grad else None
@@ -75,79 +83,49 @@ def row_groups(n, chunks, align=128):
     return out
 
 
+def _mark(timings, name, device):
+    """Records a CUDA event named `name` on the current stream (timings: list or None)."""
+    if timings is not None and device.type == "cuda":
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record(torch.cuda.current_stream(device))
+        timings.append((name, ev))
+
+
 def _vocab_parallel_sweep(be, x16, w_shard, target, cew, vocab_offset, v_global, world, group,
-                          reduce_dx):
-    """Vocab-parallel training call built on the single sweep: every rank sweeps its shard as if
-    it were a whole vocabulary (local softmax p_k, local lse_k, unit weights), and the global
-    results follow from the local ones after one exchange of five per-row numbers (lse_k, H_k, the
-    largest local logit and its global index, the target logit on its owner):
-
-        lse = logsumexp_k lse_k         a_k = e^(lse_k - lse)       (softmax = a_k p_k on shard k)
-        entropy = lse - sum_k a_k (lse_k - H_k)                     (H_k local entropy)
-        argmax: the shard whose largest logit is largest, lowest global index on equal values
-        dX = cew (sum_k a_k p_k W_k - W[target])
-
-    The local sweep returns p_k W_k - W_k[t_k] for its local target t_k; rows whose target lives on
-    another shard get local target 0 as a stand-in and the row W_k[0] is added back. On the owner
-    the two target terms combine to -(1 - a_k) W[target], with 1 - a_k formed from the other
-    shards' terms so that a confident row loses nothing to cancellation."""
-    n, h = x16.shape
+                          reduce_dx, timings=None):
+    """Vocab-parallel training call built on the single pass (formulas: csrc/head_aux.cuh).
+    Backend calls: vp_prepare (local targets, unit weights) -> train (local sweep) -> vp_pack
+    (this rank's [5, n] record) -> all-gather -> vp_combine (global statistics, this rank's share
+    of dHidden, in place) -> all-reduce."""
     dev = x16.device
     v_local = w_shard.shape[0]
-    valid = (target >= 0) & (target < v_global)
-    t_loc = target - int(vocab_offset)
-    owner = valid & (t_loc >= 0) & (t_loc < v_local)
-    local_target = torch.where(owner, t_loc, torch.where(valid, torch.zeros_like(t_loc),
-                                                         torch.full_like(t_loc, -100)))
-    ones = valid.to(torch.float32)
+    _mark(timings, "start", dev)
+    local_target, ones = be.vp_prepare(target, int(vocab_offset), v_local, int(v_global))
     out = be.train(x16, w_shard, op._bf16_weight(w_shard), local_target, ones)
-    dx1 = out["dx"]
-    # largest local logit: the logit at the local argmax
-    top = (x16.float() * w_shard.index_select(0, out["argmax"]).float()).sum(-1)
-    rec = torch.stack([out["lse"], out["entropy"], top,
-                       torch.where(owner, out["target_logit"], torch.zeros_like(top))])
-    idx_local = out["argmax"] + int(vocab_offset)
+    rec = be.vp_pack(out, target, int(vocab_offset), v_local, int(v_global))
+    _mark(timings, "sweep", dev)
     if world > 1:
-        parts = [torch.empty_like(rec) for _ in range(world)]
-        dist.all_gather(parts, rec.contiguous(), group=group)
-        allrec = torch.stack(parts)                                   # [K, 4, n]
-        idx_parts = [torch.empty_like(idx_local) for _ in range(world)]
-        dist.all_gather(idx_parts, idx_local.contiguous(), group=group)
-        allidx = torch.stack(idx_parts)                               # [K, n] exact int64 ids
+        allrec = torch.empty((world,) + tuple(rec.shape), device=rec.device, dtype=rec.dtype)
+        dist.all_gather_into_tensor(allrec.view(-1), rec.view(-1), group=group)
         me = dist.get_rank(group)
     else:
-        allrec, allidx, me = rec.unsqueeze(0), idx_local.unsqueeze(0), 0
-    lse_k, ent_k, top_k, tz_k = allrec[:, 0], allrec[:, 1], allrec[:, 2], allrec[:, 3]
-    lse = torch.logsumexp(lse_k, 0)
-    a_k = torch.exp(lse_k - lse)
-    entropy = lse - (a_k * (lse_k - ent_k)).sum(0)
-    best = top_k.max(0).values
-    cand = torch.where(top_k == best, allidx, torch.full_like(allidx, 2 ** 62))
-    argmax = cand.min(0).values
-    tz = tz_k.sum(0)
-    ce = torch.where(valid, lse - tz, torch.zeros_like(lse))
-    cw = torch.where(valid, cew, torch.zeros_like(cew))
-    loss = (cw * ce).sum()
-    metrics = torch.stack([loss, valid.sum().float(), ((argmax == target) & valid).sum().float(),
-                           torch.where(valid, entropy, torch.zeros_like(entropy)).sum()])
-    # this rank's contribution to dHidden
-    a_me = a_k[me]
-    one_minus_a = (a_k.sum(0) - a_me).clamp_min(0.0)                   # = 1 - a_me, no cancellation
-    w_t = w_shard.index_select(0, torch.where(owner, t_loc, torch.zeros_like(t_loc))).float()
-    own = owner.to(torch.float32)[:, None]
-    dx = dx1.mul_(a_me[:, None])                                       # a p_k W_k - a W_k[t_k]
-    dx.add_(w_t * ((1.0 - own) * a_me[:, None] - own * one_minus_a[:, None]))
-    dx.mul_(cw[:, None])
+        allrec, me = rec.unsqueeze(0), 0
+    _mark(timings, "exchange", dev)
+    res = be.vp_combine(allrec, me, target, cew, w_shard, int(vocab_offset), int(v_global),
+                        out["dx"])
+    _mark(timings, "combine", dev)
+    dx = out["dx"]
     if world > 1 and reduce_dx:
         dist.all_reduce(dx, op=dist.ReduceOp.SUM, group=group)
-    stats = {"lse": lse, "target_logit": torch.where(valid, tz, torch.zeros_like(tz)), "ce": ce,
-             "entropy": entropy, "argmax": argmax}
-    return loss.reshape(()), stats, dx, metrics
+    _mark(timings, "reduce", dev)
+    stats = {k: res[k] for k in _KEYS}
+    return res["loss"].reshape(()), stats, dx, res["metrics"]
 
 
 def vocab_parallel_linear_ce(x, w_shard, target, ce_weight, vocab_offset, v_global,
                              need_grad=True, group=None, backend_factory=_default_backend,
-                             reduce_dx=True, dx_chunks=1, dx_align=128, single_sweep=None):
+                             reduce_dx=True, dx_chunks=1, dx_align=128, single_sweep=None,
+                             timings=None):
     """Full-vocabulary loss / stats / dHidden from a vocabulary-sharded weight.
 
     x, target (GLOBAL ids), ce_weight are replicated on every rank; `w_shard` holds vocabulary rows
@@ -157,7 +135,9 @@ def vocab_parallel_linear_ce(x, w_shard, target, ce_weight, vocab_offset, v_glob
     (group sizes are multiples of dx_align rows, the row tile of the backward kernel).
     single_sweep (default: on when the backend has it, a gradient is wanted and dx_chunks == 1):
     each shard runs the single-sweep training kernel and the results are combined after one
-    all-gather (_vocab_parallel_sweep); otherwise forward sweep -> record exchange -> backward."""
+    all-gather (_vocab_parallel_sweep); otherwise forward sweep -> record exchange -> backward.
+    timings: a list that receives (name, CUDA event) marks at the phase boundaries of the sweep
+    form (start, sweep, exchange, combine, reduce)."""
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     x16, target, cew = _prepare(x, w_shard, target, ce_weight)
     be = backend_factory(x16, w_shard, need_grad)
@@ -165,7 +145,7 @@ def vocab_parallel_linear_ce(x, w_shard, target, ce_weight, vocab_offset, v_glob
         single_sweep = op.SINGLE_SWEEP and need_grad and dx_chunks == 1 and hasattr(be, "train")
     if single_sweep:
         loss, stats, dx, _ = _vocab_parallel_sweep(be, x16, w_shard, target, cew, vocab_offset,
-                                                   v_global, world, group, reduce_dx)
+                                                   v_global, world, group, reduce_dx, timings)
         return loss, stats, dx
     rec = be.forward_partial(x16, w_shard, target, int(vocab_offset))
     if world > 1:

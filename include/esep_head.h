@@ -194,7 +194,8 @@ size_t esep_head_step_workspace_bytes(int64_t m, int64_t h, int64_t v, int dtype
  *     selected get 0 in every output (ce / entropy are then the [B, T] per-token loss / entropy).
  * x is [m, h] in W's 16-bit type (x_dtype == dtype) or fp32 (x_dtype == ESEP_DTYPE_F32, cast
  * inside). w_bf16: a bf16 copy of W for the dHidden GEMM (pass w itself for bf16 models; may be
- * NULL when need_grad == 0). metrics[ESEP_STEP_SCALARS] and overflow may be NULL.
+ * NULL when need_grad == 0). metrics[ESEP_STEP_SCALARS], overflow and top_logit[m] (the largest
+ * logit of every selected row, exact) may be NULL.
  * overflow: device int, 1 if a row's largest logit lay more than 115 above its maximum over the
  * first 2048 vocabulary rows; the two-kernel path (esep_head_forward + esep_head_backward), which
  * this call always queues behind that flag, then replaced the sweep's results.
@@ -205,7 +206,8 @@ int esep_head_step(const void* x, int x_dtype, const void* w, const void* w_bf16
                    const int64_t* labels, const int64_t* attention_mask, int64_t seq_len,
                    int need_grad, float* lse, float* target_logit, float* ce, float* entropy,
                    int64_t* argmax, float* cew_out, float* loss, float* metrics, float* dx,
-                   int* overflow, void* workspace, size_t workspace_bytes, void* stream);
+                   float* top_logit, int* overflow, void* workspace, size_t workspace_bytes,
+                   void* stream);
 
 /* Older spelling of the flat training call: esep_head_step with target / ce_weight, a gradient
  * and the first four scalars. Same results. */
@@ -216,9 +218,41 @@ int esep_head_train(const void* x, const void* w, const void* w_bf16, const int6
                     float* cew_out, float* loss, float* metrics, float* dx, int* overflow,
                     void* workspace, size_t workspace_bytes, void* stream);
 
-/* Counters for tests: out[0] = per-device initialisations performed so far (function attributes,
+/* ---- vocabulary shards built on the single pass ------------------------------------------------
+ * Each rank runs esep_head_step on its shard of W as if it were the whole vocabulary (local
+ * softmax, unit weights, the local id of the target or 0 as a stand-in when another shard owns
+ * it), the ranks exchange one [5][n] record per rank, and esep_head_vp_combine turns the local
+ * results into this rank's share of the global ones; the shares of dx are then summed by the
+ * caller's all-reduce. The formulas are in csrc/head_aux.cuh. Replaces nothing in the reference
+ * (it is single-GPU); the merge rule is the one of solution/head/kernels.py:70-81 written for
+ * per-shard log-sum-exps. */
+
+/* local_target[n], unit_weight[n] for the shard [vocab_offset, vocab_offset + v_local). */
+int esep_head_vp_prepare(const int64_t* target, int64_t n, int64_t vocab_offset, int64_t v_local,
+                         int64_t v_global, int64_t* local_target, float* unit_weight,
+                         void* stream);
+
+/* record[5][n] of this shard from its local esep_head_step outputs: lse, entropy, largest logit,
+ * target logit (0 unless this shard owns the target), global argmax id (int32 bit for bit). */
+int esep_head_vp_pack(const float* lse, const float* entropy, const float* top_logit,
+                      const float* target_logit, const int64_t* argmax_local,
+                      const int64_t* target, int64_t n, int64_t vocab_offset, int64_t v_local,
+                      int64_t v_global, float* record, void* stream);
+
+/* records[n_records][5][n] (all shards, my_record = this shard's position) -> global lse /
+ * target_logit / ce / entropy / argmax / masked weight / loss / metrics[4], and dx[n, h]
+ * rewritten in place from the local sweep's result to this shard's share of dHidden. */
+int esep_head_vp_combine(const float* records, int n_records, int my_record,
+                         const int64_t* target, const float* ce_weight, const void* w_shard,
+                         int64_t n, int64_t h, int64_t v_local, int64_t vocab_offset,
+                         int64_t v_global, int dtype, float* dx, float* lse, float* target_logit,
+                         float* ce, float* entropy, int64_t* argmax, float* cew_out, float* loss,
+                         float* metrics, void* stream);
+
+/* Counters: out[0] = per-device initialisations performed so far (function attributes,
  * occupancy queries), out[1] = tensor maps encoded so far (maps are cached by address and
- * shape). A warmed-up process that repeats a call sees neither number move. */
+ * shape) - a warmed-up process that repeats a call sees neither number move; out[2] (n >= 3) =
+ * kernels launched by the library so far, over all entry points and threads. */
 int esep_head_debug_counters(long long* out, int n);
 
 /* ---- the step either side of the head: final residual add + RMSNorm ------------------------- */

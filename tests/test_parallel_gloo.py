@@ -41,17 +41,63 @@ class OracleBackend:
 
 
 class OracleSweepBackend(OracleBackend):
-    """Adds the single-sweep call (statistics and dHidden of the local vocabulary in one go)."""
+    """Adds the single-sweep call (statistics and dHidden of the local vocabulary in one go) and a
+    torch restatement of the three small kernels around it (csrc/head_aux.cuh: prepare, pack,
+    combine), so that the exchange logic of parallel.py runs on CPU ranks."""
 
     def train(self, x16, w16, w_bf16, target, ce_weight):
         r = self.ho.full_vocab_reference(x16, w16, target, ce_weight, want_rounded=False)
         valid = (target >= 0) & (target < w16.shape[0])
         zero = torch.zeros_like(r["lse"])
+        top = (x16.float() @ w16.float().T).max(-1).values
         return {"lse": r["lse"], "target_logit": torch.where(valid, r["tlogit"], zero),
                 "ce": torch.where(valid, r["lse"] - r["tlogit"], zero), "entropy": r["ent"],
                 "argmax": r["argmax"], "cew": torch.where(valid, ce_weight.float(), zero),
                 "loss": r["loss"].reshape(1), "metrics": torch.zeros(4), "dx": r["dx"].clone(),
-                "overflow": torch.zeros(1, dtype=torch.int32)}
+                "top": top, "overflow": torch.zeros(1, dtype=torch.int32)}
+
+    def vp_prepare(self, target, vocab_offset, v_local, v_global):
+        valid = (target >= 0) & (target < v_global)
+        t_loc = target - vocab_offset
+        owner = valid & (t_loc >= 0) & (t_loc < v_local)
+        local = torch.where(owner, t_loc, torch.where(valid, torch.zeros_like(t_loc),
+                                                      torch.full_like(t_loc, -100)))
+        return local, valid.to(torch.float32)
+
+    def vp_pack(self, out, target, vocab_offset, v_local, v_global):
+        t_loc = target - vocab_offset
+        owner = (target >= 0) & (target < v_global) & (t_loc >= 0) & (t_loc < v_local)
+        idx = (out["argmax"] + vocab_offset).to(torch.int32).view(torch.float32)
+        return torch.stack([out["lse"], out["entropy"], out["top"],
+                            torch.where(owner, out["target_logit"], torch.zeros_like(out["top"])),
+                            idx])
+
+    def vp_combine(self, records, me, target, ce_weight, w_shard, vocab_offset, v_global, dx):
+        lse_k, ent_k, top_k, tz_k = records[:, 0], records[:, 1], records[:, 2], records[:, 3]
+        idx_k = records[:, 4].contiguous().view(torch.int32).to(torch.int64)
+        lse = torch.logsumexp(lse_k, 0)
+        a_k = torch.exp(lse_k - lse)
+        entropy = lse - (a_k * (lse_k - ent_k)).sum(0)
+        best = top_k.max(0).values
+        argmax = torch.where(top_k == best, idx_k, torch.full_like(idx_k, 2 ** 62)).min(0).values
+        valid = (target >= 0) & (target < v_global)
+        tz = tz_k.sum(0)
+        zero = torch.zeros_like(lse)
+        ce = torch.where(valid, lse - tz, zero)
+        cw = torch.where(valid, ce_weight.float(), zero)
+        t_loc = target - vocab_offset
+        owner = valid & (t_loc >= 0) & (t_loc < w_shard.shape[0])
+        a_me = a_k[me]
+        a_rest = a_k.sum(0) - a_me
+        coef = torch.where(owner, -a_rest, a_me)
+        w_t = w_shard.index_select(0, torch.where(owner, t_loc, torch.zeros_like(t_loc))).float()
+        dx.mul_(a_me[:, None]).add_(w_t * coef[:, None]).mul_(cw[:, None])
+        loss = (cw * ce).sum().reshape(1)
+        metrics = torch.stack([loss[0], valid.sum().float(),
+                               ((argmax == target) & valid).sum().float(),
+                               torch.where(valid, entropy, zero).sum()])
+        return {"lse": lse, "target_logit": torch.where(valid, tz, zero), "ce": ce,
+                "entropy": entropy, "argmax": argmax, "cew": cw, "loss": loss, "metrics": metrics}
 
 
 def _inputs():
