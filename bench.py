@@ -331,7 +331,8 @@ def run_ours(args):
     ms_step = timed(lambda: step_device(record=True), args.steps, 0)
     launches1 = _counters()[2]
     clocks = sampler.stop() if rank == 0 else None
-    ms_call = statistics.mean(a.elapsed_time(b) for a, b in call_events)
+    call_ms = [a.elapsed_time(b) for a, b in call_events]
+    ms_call = statistics.mean(call_ms)
     own_launches = launches1 - launches_warm
     del launches0
 
@@ -355,7 +356,9 @@ def run_ours(args):
     f_alg = 2.0 * hv * n + 2.0 * hv * n_live
     line_extra = {}
 
-    if world == 1:
+    if world == 1 and args.only_timed:
+        pass
+    elif world == 1:
         # ---- sustained: the same step for at least two seconds, clocks sampled meanwhile ----
         sus_steps = max(50, int(2200.0 / ms_step))
         s2 = ClockSampler(local)
@@ -441,7 +444,8 @@ def run_ours(args):
                      "peak_source": peaks["source"] + " burst",
                      "flops": "algorithmic 2*H*V*N + 2*H*V*N_live (logits GEMM + dHidden GEMM, each "
                               "once); the single pass executes 4*H*V*N",
-                     "ms": ms_call,
+                     "ms": ms_call, "ms_min": min(call_ms), "ms_max": max(call_ms),
+                     "ms_first_last": [call_ms[0], call_ms[-1]],
                      "ms_note": "mean over the timed steps of the CUDA-event time of the whole "
                                 "esep_head_step call inside the timed loop (row classes, gather, "
                                 "prefix sweep, training sweep, row finish, scalars, guarded launches); "
@@ -454,7 +458,7 @@ def run_ours(args):
                  "sweep_grid": pl.bwd_grid},
     }
     line.update(line_extra)
-    if world == 1:
+    if world == 1 and not args.only_timed:
         line["cpu_baseline"] = cpu_baseline_block(cfg)
     print(json.dumps(line))
     if world > 1:
@@ -567,13 +571,59 @@ def _vocab_parallel_c4(dist, par, make_config, make_weight, shape, dev, rank, wo
     return out
 
 
+def run_norm_bandwidth(rows, hidden, iters=20):
+    """The final-norm kernels either side of the head (HBM bound) on inputs larger than L2:
+    achieved GB/s on the algorithmic bytes (forward 12 H, backward 14 H per row)."""
+    sys.path.insert(0, ROOT)
+    from esep_soup_kernels_b200.head import final_norm_backward, final_norm_forward
+
+    dev = torch.device("cuda", torch.cuda.current_device())
+    dtype = torch.float16
+    r = torch.randn(rows, hidden, device=dev)
+    d = torch.randn(rows, hidden, device=dev).to(dtype)
+    g = torch.rand(hidden, device=dev) + 0.5
+    dy = torch.randn(rows, hidden, device=dev)
+    r_out, _, rstd = final_norm_forward(r, d, g, 1e-6, dtype)
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+
+    peak = _peaks()["hbm_gbs"]
+    out = {"metric": "final-norm kernels GB/s", "rows": rows, "hidden": hidden, "dtype": "float16"}
+    for name, per_row, fn in (
+            ("forward", 12, lambda: final_norm_forward(r, d, g, 1e-6, dtype)),
+            ("backward", 14, lambda: final_norm_backward(dy, r_out, rstd, g, None, dtype))):
+        ms = timed(fn)
+        nbytes = per_row * hidden * rows
+        out[name] = {"us": ms * 1e3, "algorithmic_mb": nbytes / 1e6, "gbs": nbytes / ms / 1e6,
+                     "frac_of_measured_hbm": nbytes / ms / 1e6 / peak}
+    print(json.dumps(out))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--only-timed", action="store_true",
+                    help="one GPU: stop after the timed region and the end-to-end leg (for short "
+                         "profiler captures); the line then lacks sustained / cpu_baseline")
+    ap.add_argument("--norm-bandwidth", nargs=2, type=int, metavar=("ROWS", "HIDDEN"),
+                    help="instead of the head: time the final-norm kernels on ROWS x HIDDEN")
     args = ap.parse_args()
+    if args.norm_bandwidth:
+        run_norm_bandwidth(*args.norm_bandwidth)
+        return
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         if args.steps > 20:      # a pass over the batch takes seconds on the host

@@ -1305,6 +1305,30 @@ int esep_head_vp_combine(const float* records, int n_records, int my_record,
   return ESEP_OK;
 }
 
+int esep_head_grad_scale(const float* dx, const float* grad_loss, int64_t count, int out_dtype,
+                         void* out, void* stream) {
+  if (dx == nullptr || grad_loss == nullptr || out == nullptr || count < 0 || count % 4 != 0)
+    return ESEP_ERR_BAD_ARG;
+  if (out_dtype != ESEP_DTYPE_F16 && out_dtype != ESEP_DTYPE_BF16 && out_dtype != ESEP_DTYPE_F32)
+    return ESEP_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(dx) & 15u) || (reinterpret_cast<uintptr_t>(out) & 15u))
+    return ESEP_ERR_ALIGNMENT;
+  if (count == 0) return ESEP_OK;
+  const DeviceInfo* d = nullptr;
+  const int st = current_device_info(&d);
+  if (st != ESEP_OK) return st;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const long long n4 = count / 4;
+  const unsigned grid = static_cast<unsigned>(std::min<long long>((n4 + 255) / 256, 8LL * d->sm_count));
+  const float4* src = reinterpret_cast<const float4*>(dx);
+  if (out_dtype == ESEP_DTYPE_F16) head_grad_scale_kernel<0><<<grid, 256, 0, s>>>(src, grad_loss, n4, out);
+  else if (out_dtype == ESEP_DTYPE_BF16) head_grad_scale_kernel<1><<<grid, 256, 0, s>>>(src, grad_loss, n4, out);
+  else head_grad_scale_kernel<2><<<grid, 256, 0, s>>>(src, grad_loss, n4, out);
+  if (cudaGetLastError() != cudaSuccess) return ESEP_ERR_CUDA;
+  g_launches.fetch_add(1);
+  return ESEP_OK;
+}
+
 int esep_head_debug_counters(long long* out, int n) {
   if (out == nullptr || n < 2) return ESEP_ERR_BAD_ARG;
   out[0] = g_init_calls.load();

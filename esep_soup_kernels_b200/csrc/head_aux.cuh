@@ -301,6 +301,34 @@ __global__ void __launch_bounds__(128) head_vp_combine_kernel(const VpCombinePar
   }
 }
 
+// out[i] = dx[i] * grad_loss[0], stored as fp16 (0), bf16 (1) or fp32 (2): the whole autograd
+// backward of the op (solution/head/op.py:143-145) in one pass, grad_loss read on the device.
+template <int kOut>
+__global__ void __launch_bounds__(256)
+head_grad_scale_kernel(const float4* __restrict__ dx, const float* __restrict__ grad_loss,
+                       long long n4, void* __restrict__ out) {
+  const float g = grad_loss[0];
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float4 v = dx[i];
+    v.x *= g;
+    v.y *= g;
+    v.z *= g;
+    v.w *= g;
+    if (kOut == 2) {
+      reinterpret_cast<float4*>(out)[i] = v;
+    } else if (kOut == 0) {
+      const __half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
+      reinterpret_cast<uint2*>(out)[i] = make_uint2(*reinterpret_cast<const uint32_t*>(&a),
+                                                   *reinterpret_cast<const uint32_t*>(&b));
+    } else {
+      const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+      reinterpret_cast<uint2*>(out)[i] = make_uint2(*reinterpret_cast<const uint32_t*>(&a),
+                                                   *reinterpret_cast<const uint32_t*>(&b));
+    }
+  }
+}
+
 // Exercises the bounded-wait path on purpose: one warp waits on an mbarrier that nothing ever
 // arrives on, gives up after `limit_cycles`, records DEV_TIMEOUT_SELFTEST in the status word and
 // returns normally (no trap, the context stays usable). Used by the test suite only.

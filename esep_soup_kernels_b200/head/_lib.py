@@ -81,6 +81,7 @@ SIGNATURES = {
     "esep_head_vp_pack": (_INT, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _P, _P]),
     "esep_head_vp_combine": (_INT, [_P, _INT, _INT, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _INT,
                                     _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "esep_head_grad_scale": (_INT, [_P, _P, _I64, _INT, _P, _P]),
     "esep_head_debug_counters": (_INT, [ctypes.POINTER(ctypes.c_longlong), _INT]),
     "esep_head_norm_forward": (_INT, [_P, _P, _P, _I64, _I64, ctypes.c_float, _INT, _P, _P, _P,
                                       _P]),

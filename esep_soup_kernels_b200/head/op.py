@@ -319,6 +319,18 @@ def _run_step(x, w16, need_grad, target=None, ce_weight=None, labels=None, atten
     return out
 
 
+def _scale_grad(dx, grad_loss, dtype):
+    """(dx * grad_loss).to(dtype) in one library kernel (op.py:143-145); grad_loss stays on the
+    device."""
+    out = torch.empty(dx.shape, device=dx.device, dtype=dtype)
+    g = grad_loss.detach().to(device=dx.device, dtype=torch.float32).reshape(1)
+    with torch.cuda.device(dx.device):
+        code = _lib.load().esep_head_grad_scale(_ptr(dx), _ptr(g), dx.numel(), _X_DTYPES[dtype],
+                                                _ptr(out), _stream(dx.device))
+    _lib.check("esep_head_grad_scale", code)
+    return out
+
+
 def _prepare(x, w16, target, ce_weight):
     x16 = x.to(w16.dtype).contiguous()                       # op.py:109
     target = target.to(torch.int64).contiguous()
@@ -364,7 +376,7 @@ class FusedLinearCE(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_loss, *unused):
         (dx,) = ctx.saved_tensors
-        return (dx * grad_loss).to(ctx.x_dtype), None, None, None, None
+        return _scale_grad(dx, grad_loss, ctx.x_dtype), None, None, None, None
 
 
 def fused_linear_ce_with_metrics(x, w16, target, ce_weight, need_grad=None,

@@ -30,6 +30,43 @@ from . import _lib, op
 from .op import _KEYS, DeviceBackend, _prepare
 
 
+class RankLostError(RuntimeError):
+    """A rank of the group is gone: it announced that it left (RankRoster), or a collective of
+    the sharded forms failed or ran into the process group's timeout."""
+
+
+class RankRoster:
+    """Host-side roll call through a torch.distributed store (no GPU work, no collective).
+
+    A rank that stops taking part BETWEEN steps calls ``leave()``; the others call ``check()``
+    before they launch their next step and get a RankLostError naming the rank instead of
+    entering a collective that would never complete. A rank that disappears without announcing
+    it is caught by the collective itself (``_collective``), bounded by the group's timeout."""
+
+    def __init__(self, store, rank, world, prefix="esep_head_roster"):
+        self.store, self.rank, self.world, self.prefix = store, rank, world, prefix
+
+    def leave(self):
+        self.store.set(f"{self.prefix}/left/{self.rank}", b"1")
+
+    def check(self):
+        gone = [r for r in range(self.world)
+                if r != self.rank and self.store.check([f"{self.prefix}/left/{r}"])]
+        if gone:
+            raise RankLostError(f"rank(s) {gone} left the group")
+
+
+def _collective(fn, *args, **kwargs):
+    """Runs a torch.distributed collective; a failure (peer gone, timeout) surfaces as
+    RankLostError instead of a backend-specific exception."""
+    try:
+        return fn(*args, **kwargs)
+    except RankLostError:
+        raise
+    except RuntimeError as e:   # DistBackendError, gloo connection errors, timeouts
+        raise RankLostError(f"collective {getattr(fn, '__name__', fn)} failed: {e}") from e
+
+
 def shard_bounds(total, world, rank):
     """[lo, hi) of `rank`'s contiguous shard of `total` items, sizes differing by at most 1."""
     base, extra = divmod(total, world)
@@ -65,7 +102,7 @@ def token_sharded_linear_ce(x_local, w16, target_local, ce_weight_local, need_gr
         dx = be.backward(x16, w16, target, out["cew"], out["lse"], 0) if need_grad else None
     metrics = out["metrics"].clone()
     if dist.is_initialized() and dist.get_world_size(group) > 1:
-        dist.all_reduce(metrics, op=dist.ReduceOp.SUM, group=group)
+        _collective(dist.all_reduce, metrics, op=dist.ReduceOp.SUM, group=group)
     stats = {k: out[k] for k in _KEYS}
     return out["loss"].reshape(()), stats, dx, metrics
 
@@ -106,7 +143,7 @@ def _vocab_parallel_sweep(be, x16, w_shard, target, cew, vocab_offset, v_global,
     _mark(timings, "sweep", dev)
     if world > 1:
         allrec = torch.empty((world,) + tuple(rec.shape), device=rec.device, dtype=rec.dtype)
-        dist.all_gather_into_tensor(allrec.view(-1), rec.view(-1), group=group)
+        _collective(dist.all_gather_into_tensor, allrec.view(-1), rec.view(-1), group=group)
         me = dist.get_rank(group)
     else:
         allrec, me = rec.unsqueeze(0), 0
@@ -116,7 +153,7 @@ def _vocab_parallel_sweep(be, x16, w_shard, target, cew, vocab_offset, v_global,
     _mark(timings, "combine", dev)
     dx = out["dx"]
     if world > 1 and reduce_dx:
-        dist.all_reduce(dx, op=dist.ReduceOp.SUM, group=group)
+        _collective(dist.all_reduce, dx, op=dist.ReduceOp.SUM, group=group)
     _mark(timings, "reduce", dev)
     stats = {k: res[k] for k in _KEYS}
     return res["loss"].reshape(()), stats, dx, res["metrics"]
@@ -152,7 +189,7 @@ def vocab_parallel_linear_ce(x, w_shard, target, ce_weight, vocab_offset, v_glob
         # records are ordered by rank; ties between shards resolve to the lowest global index
         # inside the merge (argmax field carries global ids), so the order does not matter
         parts = [torch.empty_like(rec) for _ in range(world)]
-        dist.all_gather(parts, rec.contiguous(), group=group)
+        _collective(dist.all_gather, parts, rec.contiguous(), group=group)
         gathered = torch.stack(parts)
     else:
         gathered = rec.unsqueeze(0)
@@ -172,15 +209,17 @@ def vocab_parallel_linear_ce(x, w_shard, target, ce_weight, vocab_offset, v_glob
             else:
                 view.copy_(sub.backward(*args))
             # the collective starts when this group is complete and runs beside the next sweep
-            pending.append(dist.all_reduce(view, op=dist.ReduceOp.SUM, group=group, async_op=True))
+            pending.append(_collective(dist.all_reduce, view, op=dist.ReduceOp.SUM, group=group,
+                                       async_op=True))
         for work in pending:
-            work.wait()
+            _collective(work.wait)
     elif need_grad:
         dx = be.backward(x16, w_shard, target, out["cew"], out["lse"], int(vocab_offset))
         if world > 1 and reduce_dx:
-            dist.all_reduce(dx, op=dist.ReduceOp.SUM, group=group)
+            _collective(dist.all_reduce, dx, op=dist.ReduceOp.SUM, group=group)
     stats = {k: out[k] for k in _KEYS}
     return out["loss"].reshape(()), stats, dx
 
 
-__all__ = ["shard_bounds", "row_groups", "token_sharded_linear_ce", "vocab_parallel_linear_ce", "_lib"]
+__all__ = ["shard_bounds", "row_groups", "token_sharded_linear_ce", "vocab_parallel_linear_ce",
+           "RankLostError", "RankRoster", "_lib"]

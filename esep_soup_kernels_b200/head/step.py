@@ -19,7 +19,7 @@ import torch
 import torch.distributed as dist
 
 from . import _lib
-from .op import _DTYPES, _run_step
+from .op import _DTYPES, _run_step, _scale_grad
 
 IGNORE_INDEX = -100
 
@@ -87,7 +87,7 @@ class _HeadStepFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_loss, *unused):
         (dx,) = ctx.saved_tensors
-        return (dx * grad_loss).to(ctx.x_dtype), None, None, None, None
+        return _scale_grad(dx, grad_loss, ctx.x_dtype), None, None, None, None
 
 
 def causal_lm_head_step(hidden, labels, w16, attention_mask=None, num_items_in_batch=None,

@@ -249,6 +249,12 @@ int esep_head_vp_combine(const float* records, int n_records, int my_record,
                          float* ce, float* entropy, int64_t* argmax, float* cew_out, float* loss,
                          float* metrics, void* stream);
 
+/* out[count] (fp16 / bf16 / fp32 by out_dtype) = dx[count] * grad_loss[0], grad_loss a DEVICE
+ * scalar; count a multiple of 4, both arrays 16-byte aligned. One pass, no synchronisation.
+ * Replaces: FusedLinearCE.backward, solution/head/op.py:143-145 ((dx * grad_loss).to(x.dtype)). */
+int esep_head_grad_scale(const float* dx, const float* grad_loss, int64_t count, int out_dtype,
+                         void* out, void* stream);
+
 /* Counters: out[0] = per-device initialisations performed so far (function attributes,
  * occupancy queries), out[1] = tensor maps encoded so far (maps are cached by address and
  * shape) - a warmed-up process that repeats a call sees neither number move; out[2] (n >= 3) =

@@ -255,3 +255,65 @@ def test_vocab_parallel_single_sweep_composition_matches_single_process(tmp_path
         np.testing.assert_allclose(o["dx"], ref["dx"].numpy(), rtol=1e-3, atol=1e-6)
         assert np.abs(o["dx"][~valid]).max() == 0.0
     assert np.array_equal(outs[0]["dx"], outs[1]["dx"])
+
+
+def _leaving_worker(rank, world, port, announce, out_dir):
+    """Rank 1 takes part in one step and then stops, between steps, with nothing in flight; rank 0
+    goes on and must get a RankLostError within a bounded time instead of waiting forever."""
+    import datetime
+    import time
+
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=8))
+    from esep_soup_kernels_b200.head import parallel as par
+    from torch.distributed.distributed_c10d import _get_default_store
+
+    roster = par.RankRoster(_get_default_store(), rank, world)
+    x, w, t, c = _inputs()
+    lo, hi = par.shard_bounds(x.shape[0], world, rank)
+    factory = lambda x16, w16, ng: OracleBackend(x16, w16, ng)
+
+    def step():
+        roster.check()
+        return par.token_sharded_linear_ce(x[lo:hi], w, t[lo:hi], c[lo:hi], backend_factory=factory)
+
+    step()                       # a complete step with both ranks
+    dist.barrier()
+    if rank == 1:
+        if announce:
+            roster.leave()
+        dist.destroy_process_group()
+        return
+    if announce:                 # give the leaver time to post its note; no collective in between
+        deadline = time.time() + 20
+        while time.time() < deadline and not _get_default_store().check(["esep_head_roster/left/1"]):
+            time.sleep(0.05)
+    t0 = time.time()
+    try:
+        step()
+        outcome = "no error"
+    except par.RankLostError as e:
+        outcome = "RankLostError: " + str(e)[:80]
+    with open(os.path.join(out_dir, "outcome.txt"), "w") as f:
+        f.write(f"{time.time() - t0:.2f}\n{outcome}\n")
+
+
+@pytest.mark.timeout(180)
+@pytest.mark.parametrize("announce", [True, False])
+def test_a_rank_that_leaves_between_steps_ends_the_others_with_an_error(tmp_path, announce):
+    """Failure detection on the host, CPU ranks only: with a note in the store the survivor
+    learns of it before its next launch; without one the next collective fails or runs into the
+    group's (short) timeout. Either way a RankLostError, never a hang."""
+    try:
+        mp.spawn(_leaving_worker, args=(2, _free_port(), announce, str(tmp_path)), nprocs=2,
+                 join=True)
+    except Exception:   # the survivor's process group may complain while it is torn down
+        pass
+    secs, outcome = open(os.path.join(tmp_path, "outcome.txt")).read().splitlines()[:2]
+    assert outcome.startswith("RankLostError"), outcome
+    assert float(secs) < 30.0
+    if announce:
+        assert "left the group" in outcome and float(secs) < 2.0
