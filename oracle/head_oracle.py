@@ -39,7 +39,7 @@ def _as16(t, dtype):
 
 
 # ---------------------------------------------------------------------------------------------
-# solution/test_head.py:12-51  (_reference): the parity oracle BASELINE names.
+# solution/test_head.py:12-51  (_reference): the PyTorch full-vocabulary cross-entropy, the parity oracle.
 # ---------------------------------------------------------------------------------------------
 def full_vocab_reference(x, w, target, ce_weight, rows_per_step=256, want_dx=True,
                          want_rounded=True):

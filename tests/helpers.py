@@ -5,7 +5,7 @@ import torch
 
 from oracle import head_oracle as ho
 
-# Tolerances (BASELINE north star): loss and entropy 1e-3 relative, dHidden 2e-2 relative,
+# Tolerances of the parity contract: loss and entropy 1e-3 relative, dHidden 2e-2 relative,
 # argmax exact except ties. Per-row statistics get the same 1e-3 with a 1e-3 absolute floor
 # (lse and entropy are O(10); target logits can be near 0).
 LOSS_RTOL = 1e-3

@@ -166,7 +166,7 @@ def test_bad_arguments_are_rejected_on_the_host():
 
 
 def test_config1_full_vocab_fp32():
-    """BASELINE config 1: 64 rows, fp32 x, 1.5B-shape head, 10 % ignored."""
+    """Configuration 1 (the CPU reference-path check): 64 rows, fp32 x, 1.5B-shape head, 10 % ignored."""
     from esep_soup_kernels_b200.head.synthetic import make_config
 
     cfg = make_config("c1")
@@ -175,7 +175,7 @@ def test_config1_full_vocab_fp32():
 
 
 def test_config2_full_size_row_subset():
-    """BASELINE config 2 at full size; the oracle checks a seeded subset of rows (rows are
+    """Configuration 2 (8 unpadded sequences, fp16, the metric's workload) at full size; the oracle checks a seeded subset of rows (rows are
     independent) and the loss is checked through sum(ce_weight * ce)."""
     from esep_soup_kernels_b200.head.synthetic import make_config
 
@@ -191,7 +191,7 @@ def test_config2_full_size_row_subset():
 
 
 def test_config3_full_size_rows_are_independent_of_the_batch():
-    """BASELINE config 3 on one GPU (16 384 rows, bf16): a seeded row subset against the oracle, the
+    """Configuration 3 (token-sharded data parallel) on one GPU (16 384 rows, bf16): a seeded row subset against the oracle, the
     loss through sum(ce_weight * ce), and the size-independent property that a row's results do
     not depend on which other rows share the call: the 2 048 rows one GPU gets at 8 GPUs give the
     same statistics and dHidden alone as inside the full batch (the vocabulary is cut into
@@ -218,7 +218,7 @@ def test_config3_full_size_rows_are_independent_of_the_batch():
 
 
 def test_config5_edge_cases_row_subset():
-    """BASELINE config 5: x scaled x4, 50 % ignored, a zero row, planted argmax ties."""
+    """Configuration 5 (numerics edge cases, 4 099 rows): x scaled x4, 50 % ignored, a zero row, planted argmax ties."""
     from esep_soup_kernels_b200.head.synthetic import make_config
 
     cfg = make_config("c5")
@@ -262,7 +262,7 @@ def test_vocab_shards_merge_to_full_vocab_on_one_gpu(dtype):
 
 
 def test_config4_shard_shape_7b_hidden():
-    """BASELINE config 4 geometry on one shard: hidden 3584 (three passes of the backward over
+    """Configuration 4 (vocab-parallel 7B shape) geometry on one shard: hidden 3584 (three passes of the backward over
     4 x 384 columns), one of eight vocabulary shards of 152064 (19008 rows), bf16, 5 % ignored."""
     from esep_soup_kernels_b200.head.op import DeviceBackend, _KEYS
     from esep_soup_kernels_b200.head.synthetic import make_config

@@ -4,6 +4,7 @@ declares, and its planning arithmetic is sane."""
 import ctypes
 import os
 import re
+import sys
 
 import pytest
 
@@ -83,3 +84,16 @@ def test_plan_rejects_bad_sizes():
     for n, h, v in [(0, 64, 100), (10, 0, 100), (10, 64, 0), (10, 60, 100), (1 << 31, 64, 100)]:
         with pytest.raises(_lib.HeadLibraryError):
             _lib.plan_problem(n, h, v, True, 148, 33)
+
+
+def test_bench_cpu_arm_loads_the_workload_without_the_package():
+    """`bench.py --impl reference` must not map the CUDA library: it loads the synthetic workload
+    by file, so importing the package (whose import loads libesep_head.so) is never needed."""
+    import subprocess
+
+    code = ("import sys, bench; m = bench._synthetic(); "
+            "cfg = m.make_config('c1', n_override=4, v_override=64, h_override=16); "
+            "assert cfg['x'].shape == (4, 16); "
+            "assert not any(k.startswith('esep_soup_kernels_b200') for k in sys.modules), "
+            "[k for k in sys.modules if k.startswith('esep')]")
+    subprocess.run([sys.executable, "-c", code], cwd=ROOT, check=True)
