@@ -348,6 +348,35 @@ def test_argmax_is_exact_when_two_logits_are_a_few_ulp_apart():
     assert (st["argmax"].cpu() == lo).all()
 
 
+def test_metric_scalars_of_the_op_match_its_per_row_outputs():
+    """The eight scalars the kernels reduce (what a data-parallel job all-reduces instead of the
+    reference's five metric gathers, solution/head/patch.py:582-615) against the same sums formed
+    from the per-row outputs on the host."""
+    from esep_soup_kernels_b200.head import fused_linear_ce_with_metrics
+
+    x, w, t, c = _peaked(333, 128, 4001, 0.2, 12.0, 8)
+    t[::5] = -100
+    t[3] = 4001 + 7                      # out of range but not -100: labelled, no CE term
+    c[1::7] = 0.0
+    xd = x.cuda().requires_grad_(True)
+    loss, st, m = fused_linear_ce_with_metrics(xd, w.cuda(), t.cuda(), c.cuda())
+    m = m.cpu()
+    valid = (t >= 0) & (t < 4001)
+    live = valid & (c != 0)
+    ent = st["entropy"].cpu()
+    np.testing.assert_allclose(m[0], loss.item(), rtol=1e-6)
+    assert m[1] == float(valid.sum())
+    assert m[2] == float(((st["argmax"].cpu() == t) & valid).sum())
+    np.testing.assert_allclose(m[3], float(ent[valid].double().sum()), rtol=1e-5)
+    assert m[4] == float((t != -100).sum())
+    assert m[5] == float(t.numel())                       # no mask: every row counts as attended
+    np.testing.assert_allclose(m[6], float(ent.double().sum()), rtol=1e-5)
+    assert m[7] == float(live.sum())
+    with torch.no_grad():
+        _, _, m0 = fused_linear_ce_with_metrics(xd, w.cuda(), t.cuda(), c.cuda())
+    np.testing.assert_allclose(m0.cpu()[:7], m[:7], rtol=1e-5)
+
+
 def test_bf16_weight_copy_follows_the_weight_not_its_address():
     """Two training calls with same-shape fp16 weights created as temporaries (the second may
     land on the address the first one freed): each gradient must come from its own weight."""
