@@ -89,6 +89,7 @@ class _NormHead(torch.autograd.Function):
         dr, _ = final_norm_backward(dx, r_out, rstd, norm_weight)
         ctx.save_for_backward(dr)
         ctx.delta_dtype = delta.dtype if delta is not None else None
+        ctx.set_materialize_grads(False)   # no zero tensors for the outputs without gradient
         ctx.mark_non_differentiable(*stats)
         return (loss, *stats)
 

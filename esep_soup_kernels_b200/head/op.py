@@ -370,6 +370,7 @@ class FusedLinearCE(torch.autograd.Function):
         loss, stats, dx, metrics = _forward(x, w16, target, ce_weight, True, chunk_rows)
         ctx.save_for_backward(dx)
         ctx.x_dtype = x.dtype
+        ctx.set_materialize_grads(False)   # no zero tensors for the outputs without gradient
         ctx.mark_non_differentiable(*stats, metrics)
         return (loss, *stats, metrics)
 

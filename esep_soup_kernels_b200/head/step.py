@@ -80,6 +80,7 @@ class _HeadStepFn(torch.autograd.Function):
                         seq_len=seq_len)
         ctx.save_for_backward(out["dx"])
         ctx.x_dtype = hidden2d.dtype
+        ctx.set_materialize_grads(False)   # no zero tensors for the outputs without gradient
         rest = (out["ce"], out["entropy"], out["metrics"])
         ctx.mark_non_differentiable(*rest)
         return (out["loss"].reshape(()), *rest)
