@@ -19,7 +19,9 @@
 //       CTA consumes itself goes straight into its own P buffer, the other half into a 16 KiB
 //       staging area; three asynchronous bulk copies (cp.async.bulk shared::cta ->
 //       shared::cluster, 16 KiB each) then deliver the halves to the three other CTAs, counted
-//       on the receivers' mbarriers. (Per-lane remote stores were measured 6x slower.)
+//       on the receivers' per-block mbarriers; a CTA may refill its block of every P buffer as
+//       soon as both pairs' MMAs on that block have retired, while the G2 stream still works on
+//       the later blocks of the step. (Per-lane remote stores were measured 6x slower.)
 //   G2  dX^T[h, r] += sum_v W[v, h] P[v, r]        A = W tile (MN-major), B = P half (MN-major)
 // The -onehot(target) term is applied in fp32 when the accumulator is drained:
 // dX[r, :] -= ce_weight[r] * W[target[r], :]  (once, by the work unit that owns the target).
@@ -87,10 +89,10 @@ static constexpr int STAGE_BYTES = HALF_BYTES;
 static constexpr int THREADS = 256;
 static constexpr int TMEM_COLS = 512;
 static constexpr int S_COL = 384;  // logits tile lives in TMEM columns [384, 512)
-// barriers: full[6] empty[6] (slots 0..2 G1 ring, 3..5 G2 ring) s_full s_empty p_in p_peer p_empty
-//           dx_full dx_empty
-//           rd_ready rd_free stage_ready
-static constexpr int NUM_BARS = 2 * SLOTS + 10;
+static constexpr int KC_PER_BLOCK = BV / G2_KV;   // G2 K-chunks per 128-row vocabulary block
+// barriers: full[6] empty[6] (slots 0..2 G1 ring, 3..5 G2 ring) s_full s_empty p_empty
+//           dx_full dx_empty rd_ready rd_free stage_ready p_in[4] p_peer[4]
+static constexpr int NUM_BARS = 2 * SLOTS + 8 + 2 * CL;
 static constexpr int ROWDATA_BYTES = 3 * BM * 4;  // per-row c2[128], rs[128], target-local[128]
 static constexpr int SMEM_BYTES =
     1024 + P_BYTES + STAGE_BYTES + SLOTS * SLOT_BYTES + NUM_BARS * 8 + 64 + 16 + ROWDATA_BYTES;
@@ -161,14 +163,17 @@ head_bwd_kernel(const __grid_constant__ CUtensorMap tmap_x,    // x [n, h], box 
   auto ring_empty = [&](int s) { return bars + 8u * (SLOTS + s); };
   const uint32_t s_full = bars + 8u * (2 * SLOTS + 0);
   const uint32_t s_empty = bars + 8u * (2 * SLOTS + 1);
-  const uint32_t p_in = bars + 8u * (2 * SLOTS + 2);     // this CTA's P buffer holds step s
-  const uint32_t p_peer = bars + 8u * (2 * SLOTS + 3);   // leader: the peer's P buffer does too
-  const uint32_t p_empty = bars + 8u * (2 * SLOTS + 4);
-  const uint32_t dx_full = bars + 8u * (2 * SLOTS + 5);
-  const uint32_t dx_empty = bars + 8u * (2 * SLOTS + 6);
-  const uint32_t rd_ready = bars + 8u * (2 * SLOTS + 7);
-  const uint32_t rd_free = bars + 8u * (2 * SLOTS + 8);
-  const uint32_t stage_ready = bars + 8u * (2 * SLOTS + 9);
+  const uint32_t p_empty = bars + 8u * (2 * SLOTS + 2);
+  const uint32_t dx_full = bars + 8u * (2 * SLOTS + 3);
+  const uint32_t dx_empty = bars + 8u * (2 * SLOTS + 4);
+  const uint32_t rd_ready = bars + 8u * (2 * SLOTS + 5);
+  const uint32_t rd_free = bars + 8u * (2 * SLOTS + 6);
+  const uint32_t stage_ready = bars + 8u * (2 * SLOTS + 7);
+  // One barrier per 128-row vocabulary block of the P buffer (block b is produced by CTA b):
+  // p_in(b): block b of this CTA's buffer holds the current step; p_peer(b) (leader only): the
+  // pair peer's buffer does too.
+  auto p_in = [&](uint32_t b) { return bars + 8u * (2 * SLOTS + 8 + b); };
+  auto p_peer = [&](uint32_t b) { return bars + 8u * (2 * SLOTS + 8 + CL + b); };
   const int misc_off = P_BYTES + STAGE_BYTES + SLOTS * SLOT_BYTES + NUM_BARS * 8;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen_base + misc_off);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + misc_off + 8);
@@ -207,11 +212,14 @@ head_bwd_kernel(const __grid_constant__ CUtensorMap tmap_x,    // x [n, h], box 
     }
     mbar_init(s_full, 1);            // pair commit
     mbar_init(s_empty, 2 * 4);       // epilogue warps of both CTAs (leader's barrier)
-    mbar_init(p_in, 1 + 4);          // arming arrive + local epilogue warps (+ 48 KiB of copies)
-    mbar_init(p_peer, 1);            // relay arrive from the pair peer
+    for (uint32_t b = 0; b < CL; ++b) {
+      // own block: the four epilogue warps that write it; other blocks: the arming arrive (+ 16 KiB)
+      mbar_init(p_in(b), b == c ? 4 : 1);
+      mbar_init(p_peer(b), 1);       // relay arrive from the pair peer
+    }
     mbar_init(rd_free, 4);           // epilogue warps of this CTA
     mbar_init(stage_ready, 4);       // epilogue warps of this CTA
-    mbar_init(p_empty, 2);           // one commit per pair
+    mbar_init(p_empty, 2);           // one commit per pair, after THIS CTA's block is consumed
     mbar_init(dx_full, 1);           // pair commit
     mbar_init(dx_empty, 2 * 4);      // epilogue warps of both CTAs (leader's barrier)
     mbar_init(rd_ready, 128);        // epilogue threads of this CTA
@@ -377,26 +385,34 @@ head_bwd_kernel(const __grid_constant__ CUtensorMap tmap_x,    // x [n, h], box 
       constexpr uint32_t idesc2 = make_idesc(kFmt, 256, BM, 1, 1);  // MN-major A and B
       uint32_t stage = 0, phase = 0, g2par = 0, upar = 0;
       bool ok = true;
+      if (elected)   // first step: 16 KiB from each of the three other CTAs
+        for (uint32_t b = 0; b < CL; ++b)
+          if (b != c) mbar_expect_tx(p_in(b), HALF_BYTES);
       for (long long u = u_first; u < u_last && ok; u = unit_next(u)) {
         int s0, s1;
         unit_steps(u, s0, s1);
         for (int step = s0; step < s1 && ok; ++step) {
-          // P of this step: the local buffer (own epilogue + three bulk copies) and the peer's
-          if (elected) mbar_expect_tx(p_in, 3 * HALF_BYTES);
-          ok = mbar_wait_warp<true>(p_in, g2par, abort_flag) &&
-               mbar_wait_warp<true>(p_peer, g2par, abort_flag);
-          if (!ok) break;
-          fence_proxy_async();
-          tc_fence_after();
-          if (step == s0) {  // the previous unit's dX must be drained before we overwrite it
-            ok = mbar_wait_warp<true>(dx_empty, upar ^ 1u, abort_flag);
-            if (!ok) break;
-            tc_fence_after();
-          }
           // B = P half: one 128-byte line per vocabulary row, 8-row groups 1024 B apart.
           uint64_t bdesc = make_smem_desc(p_base, 8192, 1024);
           uint32_t acc0 = (step == s0) ? 0u : 1u;
           for (int kc = 0; kc < STEP_V / G2_KV; ++kc) {
+            if ((kc & (KC_PER_BLOCK - 1)) == 0) {
+              // block b of P (from CTA b) must be in this CTA's buffer and in the peer's
+              const uint32_t b = static_cast<uint32_t>(kc / KC_PER_BLOCK);
+              ok = mbar_wait_warp<true>(p_in(b), g2par, abort_flag) &&
+                   mbar_wait_warp<true>(p_peer(b), g2par, abort_flag);
+              if (!ok) break;
+              // arm the block's barrier for the next step: its data can only be sent after this
+              // step's MMAs on the block have retired (p_empty), so the arming always comes first
+              if (elected && b != c) mbar_expect_tx(p_in(b), HALF_BYTES);
+              fence_proxy_async();
+              tc_fence_after();
+              if (step == s0 && kc == 0) {  // the previous unit's dX must be drained first
+                ok = mbar_wait_warp<true>(dx_empty, upar ^ 1u, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+              }
+            }
             ok = mbar_wait_warp<true>(ring_full(SLOTS_A + stage), phase, abort_flag);
             if (!ok) break;
             tc_fence_after();
@@ -411,6 +427,10 @@ head_bwd_kernel(const __grid_constant__ CUtensorMap tmap_x,    // x [n, h], box 
                 umma_f16_ss_pair(d, adesc + 512u * hb + 128u, bdesc + 128u, idesc2, 1u);
               }
               umma_commit_pair_mask(ring_empty(SLOTS_A + stage), pair_mask);
+              // block kc / 4 of every P buffer this pair reads is free once these MMAs retire:
+              // tell the CTA that produces it (the other pair's commit completes its barrier)
+              if ((kc & (KC_PER_BLOCK - 1)) == KC_PER_BLOCK - 1)
+                umma_commit_pair_mask(p_empty, static_cast<uint16_t>(1u << (kc / KC_PER_BLOCK)));
             }
             acc0 = 1u;
             bdesc += 256u;  // next 32 vocabulary lines of P
@@ -419,8 +439,6 @@ head_bwd_kernel(const __grid_constant__ CUtensorMap tmap_x,    // x [n, h], box 
               phase ^= 1u;
             }
           }
-          // every P buffer of the cluster is free once both pairs' MMAs retire
-          if (ok && elected) umma_commit_pair_mask(p_empty, static_cast<uint16_t>(0xF));
           g2par ^= 1u;
         }
         if (ok && elected) umma_commit_pair_mask(dx_full, pair_mask);
@@ -434,17 +452,24 @@ head_bwd_kernel(const __grid_constant__ CUtensorMap tmap_x,    // x [n, h], box 
       // Pair peer: no MMAs to issue. This warp arms the local P barrier each step and relays
       // its completion to the leader, whose MMAs read this CTA's P buffer as well.
       const bool elected = elect_one_sync();
-      const uint32_t p_peer_leader = mapa_shared(p_peer, leader);
+      const uint32_t p_peer_leader0 = mapa_shared(p_peer(0), leader);
       uint32_t par = 0;
       bool ok = true;
+      if (elected)
+        for (uint32_t b = 0; b < CL; ++b)
+          if (b != c) mbar_expect_tx(p_in(b), HALF_BYTES);
       for (long long u = u_first; u < u_last && ok; u = unit_next(u)) {
         int s0, s1;
         unit_steps(u, s0, s1);
-        for (int s = s0; s < s1; ++s) {
-          if (elected) mbar_expect_tx(p_in, 3 * HALF_BYTES);
-          ok = mbar_wait_warp<true>(p_in, par, abort_flag);
-          if (!ok) break;
-          if (elected) mbar_arrive_remote(p_peer_leader);
+        for (int s = s0; s < s1 && ok; ++s) {
+          for (uint32_t b = 0; b < CL; ++b) {
+            ok = mbar_wait_warp<true>(p_in(b), par, abort_flag);
+            if (!ok) break;
+            if (elected) {
+              mbar_arrive_remote(p_peer_leader0 + 8u * b);
+              if (b != c) mbar_expect_tx(p_in(b), HALF_BYTES);   // next step (see the leader)
+            }
+          }
           par ^= 1u;
         }
       }
@@ -557,7 +582,7 @@ head_bwd_kernel(const __grid_constant__ CUtensorMap tmap_x,    // x [n, h], box 
         fence_proxy_async();  // the lines are read by the async proxy (bulk copies, MMAs)
         __syncwarp();
         if (lane == 0) {
-          mbar_arrive(p_in);         // the own block of the own buffer is in place
+          mbar_arrive(p_in(c));      // a quarter of the own block of the own buffer is in place
           mbar_arrive(stage_ready);
         }
         if (copy_warp) {
@@ -565,12 +590,12 @@ head_bwd_kernel(const __grid_constant__ CUtensorMap tmap_x,    // x [n, h], box 
           if (copy_lane) {
             // own half -> the CTA of the other pair that consumes the same rows
             bulk_copy_to_cluster(mapa_shared(own_block, c ^ 2u), own_block, HALF_BYTES,
-                                 mapa_shared(p_in, c ^ 2u));
+                                 mapa_shared(p_in(c), c ^ 2u));
             // staged half -> the two CTAs that consume the other rows
             bulk_copy_to_cluster(mapa_shared(own_block, c ^ 1u), stage_buf, HALF_BYTES,
-                                 mapa_shared(p_in, c ^ 1u));
+                                 mapa_shared(p_in(c), c ^ 1u));
             bulk_copy_to_cluster(mapa_shared(own_block, c ^ 3u), stage_buf, HALF_BYTES,
-                                 mapa_shared(p_in, c ^ 3u));
+                                 mapa_shared(p_in(c), c ^ 3u));
           }
         }
         return true;
@@ -589,12 +614,12 @@ head_bwd_kernel(const __grid_constant__ CUtensorMap tmap_x,    // x [n, h], box 
         while (ok && !(stored && drained)) {
           // every consumer must be done with the previous contents of its P buffer
           if (!stored &&
-              __all_sync(0xffffffffu, mbar_try_wait_cluster(p_empty, (scount & 1u) ^ 1u))) {
+              __all_sync(0xffffffffu, mbar_test_wait_cluster(p_empty, (scount & 1u) ^ 1u))) {
             ok = hand_over();
             stored = true;
           }
           if (ok && !drained &&
-              __all_sync(0xffffffffu, mbar_try_wait_cluster(s_full, (scount + 1u) & 1u))) {
+              __all_sync(0xffffffffu, mbar_test_wait_cluster(s_full, (scount + 1u) & 1u))) {
             drain_logits();
             drained = true;
           }

@@ -77,7 +77,6 @@ struct TrainParams {
 namespace trn {
 using namespace bwd;
 static constexpr int EPI_WARPS = 8;
-static constexpr int KC_PER_BLOCK = BV / G2_KV;   // G2 K-chunks per 128-row vocabulary block
 static constexpr int THREADS_T = 128 + EPI_WARPS * 32;   // 384
 static constexpr float REF_MARGIN = 40.f;      // added to the prefix maximum: the reference m_ref
 static constexpr float OVERFLOW_NATS = 75.f;   // largest z - m_ref the sweep accepts
