@@ -18,6 +18,7 @@
 #include "head_norm.cuh"
 #include "head_step.cuh"
 #include "head_train.cuh"
+#include "head_train_wide.cuh"
 
 using namespace esep;
 
@@ -29,6 +30,7 @@ constexpr size_t kAlign = 256;
 
 struct DeviceInfo {
   int cc_major = 0, cc_minor = 0, sm_count = 0, max_clusters_bwd = 0, max_pairs_fwd = 0;
+  int max_clusters_wide = 0;   // resident 8-CTA clusters of head_train_wide_kernel (0: not available)
   int init_status = ESEP_ERR_CUDA;
 };
 
@@ -41,6 +43,7 @@ DeviceInfo g_info[kMaxDevices];
 PFN_cuTensorMapEncodeTiled g_encode = nullptr;
 std::atomic<long long> g_init_calls{0};   // completed per-device initialisations (test aid)
 std::atomic<long long> g_launches{0};     // kernels this library has launched (all entry points)
+std::atomic<long long> g_wide_launches{0};   // of head_train_wide_kernel
 
 size_t align_up(size_t x) { return (x + kAlign - 1) / kAlign * kAlign; }
 
@@ -130,6 +133,29 @@ bool init_device(int device) {
       d.max_clusters_bwd = std::min(ncl, d.sm_count / kBwdCluster);
     else
       ok = false;
+  }
+  if (ok) {
+    // How many 8-CTA clusters of the wide training kernel can be resident at once. A device that
+    // cannot place one keeps the 4-CTA kernel for every hidden size: not an error.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(d.sm_count / trnw::CLW * trnw::CLW));
+    cfg.blockDim = dim3(trn::THREADS_T);
+    cfg.dynamicSmemBytes = trn::SMEM_BYTES_T;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = trnw::CLW;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int ncl = 0;
+    if (cudaFuncSetAttribute(head_train_wide_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             trn::SMEM_BYTES_T) == cudaSuccess &&
+        cudaFuncSetAttribute(head_train_wide_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             trn::SMEM_BYTES_T) == cudaSuccess &&
+        cudaOccupancyMaxActiveClusters(&ncl, head_train_wide_kernel<0>, &cfg) == cudaSuccess &&
+        ncl > 0)
+      d.max_clusters_wide = std::min(ncl, d.sm_count / trnw::CLW);
   }
   cudaGetLastError();
   cudaSetDevice(prev);
@@ -831,6 +857,10 @@ constexpr int64_t kPrefixRows = 2048;   // vocabulary prefix that gives the per-
 struct StepLayout {
   esep_head_plan pl;   // host plan for all m rows with gradient
   int ncl;             // clusters of the training sweep launch
+  bool wide;           // the sweep runs as 8-CTA clusters (head_train_wide_kernel), one pass
+  int nhb_a, nhb_b;    // wide: accumulator blocks per producer / consumer CTA
+  int rows_nhb;        // accumulator blocks per quarter of a pass, as the row-finish kernel sees it
+  int pass_w;          // columns per pass = row stride of the partial dHidden pieces
   int part_cap;        // rows of the forward partial arrays
   size_t base_bytes;
   size_t record_off, st_off, st_stride, lo_off, lo_stride, dxpart_off, xc_off, tgtc_off, tgto_off,
@@ -848,6 +878,25 @@ int step_layout(int64_t m, int64_t h, int64_t v, bool need_grad, const DeviceInf
   if (st != ESEP_OK) return st;
   const esep_head_plan& pl = t->pl;
   t->ncl = pl.bwd_grid / kBwdCluster;
+  t->wide = false;
+  t->nhb_a = t->nhb_b = 0;
+  t->rows_nhb = pl.bwd_hblocks;
+  t->pass_w = kBwdCluster * pl.bwd_hslice;
+  // Hidden sizes of three passes whose accumulator fits eight SMs (28 blocks of 128 columns). With
+  // two passes the 4-CTA kernel is the faster one (measured: 645 - 670 against 561 - 614 TFLOP/s
+  // algorithmic at 2048 - 3072 columns; at 3584: 456 against 621).
+  if (need_grad && d->max_clusters_wide > 0 && pl.bwd_passes > 2 && h % 128 == 0 &&
+      h <= 28 * 128) {
+    const int blocks = static_cast<int>(h / 128);
+    t->wide = true;
+    t->nhb_a = div_up(std::max(blocks - 16, 1), 4);
+    t->nhb_b = div_up(blocks - 4 * t->nhb_a, 4);
+    t->rows_nhb = div_up(blocks, 4);
+    t->pass_w = 4 * t->rows_nhb * 128;
+    const int64_t n_tp = div_up(m, 128);
+    t->ncl = static_cast<int>(
+        std::min<int64_t>(d->max_clusters_wide, n_tp * pl.bwd_total_steps));
+  }
   const size_t mr = static_cast<size_t>(div_up(m, 256)) * 256;
   t->part_cap = static_cast<int>(std::min<size_t>(mr + static_cast<size_t>(4) * 256 * d->max_pairs_fwd,
                                                   static_cast<size_t>(1) << 30));
@@ -878,7 +927,7 @@ int step_layout(int64_t m, int64_t h, int64_t v, bool need_grad, const DeviceInf
     // a left-over pair is cut into at most ncl / rem_tp runs: rem_tp * rem_splits <= ncl
     t->lo_stride = align_up(static_cast<size_t>(16) * 128 * t->ncl * f4);
     t->lo_off = take(4 * t->lo_stride);
-    t->dxpart_off = take(static_cast<size_t>(t->ncl) * 128 * kBwdCluster * pl.bwd_hslice * f4);
+    t->dxpart_off = take(static_cast<size_t>(t->ncl) * 128 * t->pass_w * f4);
     t->dxc_off = take(static_cast<size_t>(m) * h * f4);
     t->fb_stride = align_up(static_cast<size_t>(m) * f4);
     t->fb_off = take(5 * t->fb_stride);
@@ -1024,7 +1073,7 @@ int step_impl(const StepArgs& a) {
     if (st != ESEP_OK) return st;
 
     // 4. the training sweep over the compact rows [0, n_sweep)
-    CUtensorMap tx, tw1, tw2;
+    CUtensorMap tx, tw1, tw2, tw2b;
     if (make_tmap(&tx, xc, a.dtype, a.m, a.h, bwd::BK, 64) != ESEP_OK) return ESEP_ERR_CUDA;
     if (make_tmap(&tw1, a.w, a.dtype, a.v, a.h, bwd::BK, bwd::BV) != ESEP_OK) return ESEP_ERR_CUDA;
     const bool w2_is_3d = (a.h % 64 == 0);
@@ -1055,11 +1104,44 @@ int step_impl(const StepArgs& a) {
     p.w2_is_3d = w2_is_3d ? 1 : 0;
     p.overflow = overflow;
     p.status = status;
-    st = a.dtype == ESEP_DTYPE_F16
-             ? launch_cluster(head_train_kernel<0>, static_cast<unsigned>(pl.bwd_grid),
-                              trn::THREADS_T, trn::SMEM_BYTES_T, kBwdCluster, s, tx, tw1, tw2, p)
-             : launch_cluster(head_train_kernel<1>, static_cast<unsigned>(pl.bwd_grid),
-                              trn::THREADS_T, trn::SMEM_BYTES_T, kBwdCluster, s, tx, tw1, tw2, p);
+    if (t.wide) {
+      // one pass on 8-CTA clusters: same arrays, same work split, other geometry
+      if (make_tmap_w3(&tw2, a.w_bf16, ESEP_DTYPE_BF16, a.v, a.h, bwd::G2_KV, 2 * t.nhb_a) !=
+              ESEP_OK ||
+          make_tmap_w3(&tw2b, a.w_bf16, ESEP_DTYPE_BF16, a.v, a.h, bwd::G2_KV, 2 * t.nhb_b) !=
+              ESEP_OK)
+        return ESEP_ERR_CUDA;
+      TrainWideParams pw = {};
+      pw.n = m;
+      pw.h = h;
+      pw.v = v;
+      pw.n_dev = p.n_dev;
+      pw.nhb_a = t.nhb_a;
+      pw.nhb_b = t.nhb_b;
+      pw.pass_w = t.pass_w;
+      pw.total_steps = p.total_steps;
+      pw.m_ref = p.m_ref;
+      pw.target = p.target;
+      pw.dx = p.dx;
+      pw.dx_part = p.dx_part;
+      pw.st_s = p.st_s; pw.st_t = p.st_t; pw.st_max = p.st_max; pw.st_idx = p.st_idx;
+      pw.lo_s = p.lo_s; pw.lo_t = p.lo_t; pw.lo_max = p.lo_max; pw.lo_idx = p.lo_idx;
+      pw.overflow = overflow;
+      pw.status = status;
+      const unsigned grid = static_cast<unsigned>(t.ncl * trnw::CLW);
+      st = a.dtype == ESEP_DTYPE_F16
+               ? launch_cluster(head_train_wide_kernel<0>, grid, trn::THREADS_T, trn::SMEM_BYTES_T,
+                                trnw::CLW, s, tx, tw1, tw2, tw2b, pw)
+               : launch_cluster(head_train_wide_kernel<1>, grid, trn::THREADS_T, trn::SMEM_BYTES_T,
+                                trnw::CLW, s, tx, tw1, tw2, tw2b, pw);
+      if (st == ESEP_OK) g_wide_launches.fetch_add(1);
+    } else {
+      st = a.dtype == ESEP_DTYPE_F16
+               ? launch_cluster(head_train_kernel<0>, static_cast<unsigned>(pl.bwd_grid),
+                                trn::THREADS_T, trn::SMEM_BYTES_T, kBwdCluster, s, tx, tw1, tw2, p)
+               : launch_cluster(head_train_kernel<1>, static_cast<unsigned>(pl.bwd_grid),
+                                trn::THREADS_T, trn::SMEM_BYTES_T, kBwdCluster, s, tx, tw1, tw2, p);
+    }
     if (st != ESEP_OK) return st;
   }
 
@@ -1125,7 +1207,7 @@ int step_impl(const StepArgs& a) {
   r.h = h;
   r.v = v;
   r.n_clusters = t.ncl;
-  r.nhb = pl.bwd_hblocks;
+  r.nhb = t.rows_nhb;
   r.total_steps = pl.bwd_total_steps;
   r.n_vtiles = pl.fwd_vocab_tiles;
   r.fwd_pairs = static_cast<int>(fwd_grid / 2);
@@ -1334,6 +1416,7 @@ int esep_head_debug_counters(long long* out, int n) {
   out[0] = g_init_calls.load();
   out[1] = g_tmap_encodes.load();
   if (n >= 3) out[2] = g_launches.load();
+  if (n >= 4) out[3] = g_wide_launches.load();
   return ESEP_OK;
 }
 

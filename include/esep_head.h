@@ -258,7 +258,8 @@ int esep_head_grad_scale(const float* dx, const float* grad_loss, int64_t count,
 /* Counters: out[0] = per-device initialisations performed so far (function attributes,
  * occupancy queries), out[1] = tensor maps encoded so far (maps are cached by address and
  * shape) - a warmed-up process that repeats a call sees neither number move; out[2] (n >= 3) =
- * kernels launched by the library so far, over all entry points and threads. */
+ * kernels launched by the library so far, over all entry points and threads; out[3] (n >= 4) =
+ * how many of those were the 8-CTA-cluster training sweep (hidden sizes of 3200 - 3584). */
 int esep_head_debug_counters(long long* out, int n);
 
 /* ---- the step either side of the head: final residual add + RMSNorm ------------------------- */

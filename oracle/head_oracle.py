@@ -323,7 +323,7 @@ def step_from_logits(hidden, w, labels, want_grad=False):
         correct = ((logits.argmax(dim=-1) == target) & valid).sum()
     out.update({"token_loss": token_loss.detach(), "token_entropy": token_entropy,
                 "correct": int(correct), "labelled": int(valid.sum()),
-                "loss_mean": float(loss_mean)})
+                "loss_mean": float(loss_mean.detach())})
     return out
 
 

@@ -274,6 +274,40 @@ def test_config4_shard_shape_7b_hidden():
     check_against_oracle(x, w, t, c, loss, stats, dx)
 
 
+@pytest.mark.parametrize("n,h,v,dtype", [
+    (300, 3584, 5003, torch.float16),      # three row tiles, each cut into vocabulary runs
+    (2700, 3584, 3000, torch.bfloat16),    # 22 row tiles: full rounds on every cluster + a left-over
+    (260, 3200, 2100, torch.bfloat16),     # 25 accumulator blocks: the last CTA's slice is ragged
+])
+def test_hidden_of_three_passes_runs_as_one_pass_on_eight_cta_clusters(n, h, v, dtype):
+    """Hidden sizes whose dHidden accumulator needs three passes of the 4-CTA sweep (3200 - 3584
+    columns) run on 8-CTA clusters that hold the whole accumulator: four CTAs compute logits and
+    P, all eight accumulate dHidden, every logits tile is computed once. Same results as any
+    other size; the library's counter shows that this kernel ran."""
+    import ctypes
+    from esep_soup_kernels_b200.head import _lib
+
+    def wide_launches():
+        buf = (ctypes.c_longlong * 4)()
+        assert _lib.load().esep_head_debug_counters(buf, 4) == 0
+        return buf[3]
+
+    g = torch.Generator().manual_seed(n + h + v)
+    w = (torch.randn(v, h, generator=g) * (1.0 / h ** 0.5)).to(dtype)
+    x = torch.randn(n, h, generator=g).to(dtype)
+    t = torch.randint(0, v, (n,), generator=g)
+    t[::17] = -100
+    c = torch.rand(n, generator=g)
+    c[t < 0] = 0.0
+    before = wide_launches()
+    loss, stats, dx = run_op(x, w, t, c)
+    assert wide_launches() == before + 1
+    check_against_oracle(x, w, t, c, loss, stats, dx)
+    assert dx[::17].abs().max().item() == 0.0
+    loss2, stats2, dx2 = run_op(x, w, t, c)
+    assert torch.equal(loss, loss2) and torch.equal(dx, dx2)
+
+
 def test_rows_without_a_loss_term_take_the_forward_sweep_and_get_zero_gradient():
     """With many ignored rows the library sweeps only the live rows for the gradient and gives
     the others their statistics from a forward sweep (the reference orders the live rows first
@@ -534,12 +568,12 @@ def test_causal_lm_head_step_matches_the_logits_path():
     assert step_metrics(step4)["num_tokens"] == bsz * seq
 
 
-def _planted_outlier_case(scale):
+def _planted_outlier_case(scale, h=64):
     """One row whose logit at a vocabulary index past the 2 048-row prefix is about `scale`, far
     above everything the prefix holds."""
     g = torch.Generator().manual_seed(17)
-    n, h, v = 150, 64, 5000
-    w = (torch.randn(v, h, generator=g) * 0.3).half()
+    n, v = 150, 5000
+    w = (torch.randn(v, h, generator=g) * 0.3 * (64.0 / h) ** 0.5).half()
     x = torch.randn(n, h, generator=g).half()
     t = torch.randint(0, v, (n,), generator=g)
     c = torch.rand(n, generator=g)
@@ -569,6 +603,11 @@ def test_single_sweep_falls_back_when_a_row_maximum_is_far_above_the_prefix():
         loss, stats, dx = run_op(x, w, t, c)
         assert not last_call_fell_back("cuda:0")
         check_against_oracle(x, w, t, c, loss, stats, dx)
+    # the same guard behind the 8-CTA-cluster sweep (hidden 3584)
+    x, w, t, c = _planted_outlier_case(600.0, h=3584)
+    loss, stats, dx = run_op(x, w, t, c)
+    assert last_call_fell_back("cuda:0")
+    check_against_oracle(x, w, t, c, loss, stats, dx)
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
