@@ -1119,6 +1119,7 @@ int step_impl(const StepArgs& a) {
       pw.nhb_a = t.nhb_a;
       pw.nhb_b = t.nhb_b;
       pw.pass_w = t.pass_w;
+      pw.slots_a = 4;   // measured at 3584 columns: 2 / 3 / 4 / 5 slots -> 389 / 562 / 640 / 612 TFLOP/s
       pw.total_steps = p.total_steps;
       pw.m_ref = p.m_ref;
       pw.target = p.target;

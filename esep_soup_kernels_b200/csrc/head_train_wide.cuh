@@ -27,6 +27,7 @@ struct TrainWideParams {
   int nhb_a;              // accumulator blocks per producer CTA (1..3)
   int nhb_b;              // accumulator blocks per consumer CTA (1..4)
   int pass_w;             // row stride of the partial pieces (>= h)
+  int slots_a;            // ring slots of the producers' G1 stream (2 .. SLOTS - 2)
   int total_steps;
   const float* m_ref;
   const long long* target;
@@ -109,6 +110,10 @@ head_train_wide_kernel(const __grid_constant__ CUtensorMap tmap_x,    // x [n, h
   // vocabulary run per cluster for the left-over tiles).
   const int n_clusters = gridDim.x / CLW;
   const int nhb = prod ? p.nhb_a : p.nhb_b;   // accumulator blocks of this CTA
+  // producers' ring: slots [0, slots_a) feed G1, the other SLOTS - slots_a feed G2. G1 moves 3.5
+  // times the bytes of G2 here, so it gets more of the slots than in head_train_kernel.
+  const uint32_t slots_a = static_cast<uint32_t>(p.slots_a);
+  const uint32_t slots_b = static_cast<uint32_t>(SLOTS) - slots_a;
   // first hidden column of this CTA: producers' slices first, then the consumers'
   const int hs0 = prod ? static_cast<int>(c) * p.nhb_a * 128
                        : CL * p.nhb_a * 128 + (static_cast<int>(c) - CL) * p.nhb_b * 128;
@@ -196,7 +201,7 @@ head_train_wide_kernel(const __grid_constant__ CUtensorMap tmap_x,    // x [n, h
             tma_load_2d_pair(sa, &tmap_w1, bar, kb * BK, vrow);
             tma_load_2d_pair(sa + 16384, &tmap_x, bar, kb * BK, xrow);
           }
-          if (++stage == SLOTS_A) {
+          if (++stage == slots_a) {
             stage = 0;
             phase ^= 1u;
           }
@@ -213,11 +218,11 @@ head_train_wide_kernel(const __grid_constant__ CUtensorMap tmap_x,    // x [n, h
     const bool elected = elect_one_sync();
     uint32_t stage = 0, phase = 0;
     bool ok = true;
-    // producers: ring slots SLOTS_A.. of 24 KiB; consumers: CSLOTS slots of 32 KiB from stage_buf
-    const int first = prod ? SLOTS_A : 0;
-    const uint32_t n_stages = prod ? SLOTS_B : CSLOTS;
+    // producers: ring slots slots_a.. of 24 KiB; consumers: CSLOTS slots of 32 KiB from stage_buf
+    const int first = prod ? static_cast<int>(slots_a) : 0;
+    const uint32_t n_stages = prod ? slots_b : CSLOTS;
     const uint32_t slot_bytes = prod ? SLOT_BYTES : CSLOT_BYTES;
-    const uint32_t ring0 = prod ? ring + SLOTS_A * SLOT_BYTES : stage_buf;
+    const uint32_t ring0 = prod ? ring + slots_a * SLOT_BYTES : stage_buf;
     const uint32_t tx_bytes = static_cast<uint32_t>(nhb) * 8192u;   // the box holds nhb blocks
     const uint32_t full_leader0 = mapa_shared(ring_full(first), leader);
     for (long long u = u_first; u < u_last && ok; u = unit_next(u)) {
@@ -275,7 +280,7 @@ head_train_wide_kernel(const __grid_constant__ CUtensorMap tmap_x,    // x [n, h
               umma_f16_ss_pair(d, adesc + 6u, bdesc + 6u, idesc1, 1u);
               umma_commit_pair_mask(ring_empty(stage), pair_mask);
             }
-            if (++stage == SLOTS_A) {
+            if (++stage == slots_a) {
               stage = 0;
               phase ^= 1u;
             }
@@ -296,10 +301,10 @@ head_train_wide_kernel(const __grid_constant__ CUtensorMap tmap_x,    // x [n, h
       constexpr uint32_t idesc2 = make_idesc(1, 256, BM, 1, 1);  // bf16, MN-major A and B
       uint32_t stage = 0, phase = 0, g2par = 0, upar = 0;
       bool ok = true;
-      const int first = prod ? SLOTS_A : 0;
-      const uint32_t n_stages = prod ? SLOTS_B : CSLOTS;
+      const int first = prod ? static_cast<int>(slots_a) : 0;
+      const uint32_t n_stages = prod ? slots_b : CSLOTS;
       const uint32_t slot_bytes = prod ? SLOT_BYTES : CSLOT_BYTES;
-      const uint32_t ring0 = prod ? ring + SLOTS_A * SLOT_BYTES : stage_buf;
+      const uint32_t ring0 = prod ? ring + slots_a * SLOT_BYTES : stage_buf;
       if (elected)   // first step: 16 KiB from every producer other than this CTA
         for (uint32_t b = 0; b < CL; ++b)
           if (b != c) mbar_expect_tx(p_in(b), HALF_BYTES);
