@@ -631,6 +631,48 @@ def run_norm_bandwidth(rows, hidden, iters=20):
     print(json.dumps(out))
 
 
+def run_shape(rows, hidden, vocab, steps, warmup):
+    """fused_linear_ce + backward on a synthetic bf16 problem of the given shape on one GPU (e.g.
+    one vocabulary shard of the 7B configuration: 32768 3584 19008): ms per step with a CUDA
+    event pair, algorithmic TFLOP/s (4 H V per row) and its share of the measured tensor peak.
+    A profiler capture of a kernel at another hidden size uses this with few rows."""
+    sys.path.insert(0, ROOT)
+    from esep_soup_kernels_b200.head import fused_linear_ce, last_device_status
+
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(rows, hidden, generator=g).to(torch.bfloat16).to(dev)
+    w = torch.empty(vocab, hidden, dtype=torch.bfloat16, device=dev)
+    for lo in range(0, vocab, 16384):      # the weight is built in slices: no fp32 copy of it
+        n = min(16384, vocab - lo)
+        w[lo:lo + n] = (torch.randn(n, hidden, generator=g) * 0.02).to(torch.bfloat16).to(dev)
+    t = torch.randint(0, vocab, (rows,), generator=g).to(dev)
+    c = torch.full((rows,), 1.0 / rows, device=dev)
+
+    def step():
+        xg = x.detach().requires_grad_(True)
+        loss, _ = fused_linear_ce(xg, w, t, c)
+        loss.backward()
+        return loss
+
+    for _ in range(max(warmup, 1)):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        loss = step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    tf = 4.0 * hidden * vocab * rows / (ms * 1e-3) / 1e12
+    print(json.dumps({"metric": "head step on a given shape", "rows": rows, "hidden": hidden,
+                      "vocab": vocab, "dtype": "bfloat16", "steps": steps, "ms_per_step": ms,
+                      "rows_s": rows / (ms * 1e-3), "algorithmic_tflops": tf,
+                      "frac_of_measured_tensor_peak": tf / _peaks()["tflops"],
+                      "loss": float(loss.detach()), "device_status": last_device_status()}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -642,9 +684,14 @@ def main():
                          "profiler captures); the line then lacks sustained / cpu_baseline")
     ap.add_argument("--norm-bandwidth", nargs=2, type=int, metavar=("ROWS", "HIDDEN"),
                     help="instead of the head: time the final-norm kernels on ROWS x HIDDEN")
+    ap.add_argument("--shape", nargs=3, type=int, metavar=("ROWS", "HIDDEN", "VOCAB"),
+                    help="instead of configuration 2: time the head step (bf16) on this shape")
     args = ap.parse_args()
     if args.norm_bandwidth:
         run_norm_bandwidth(*args.norm_bandwidth)
+        return
+    if args.shape:
+        run_shape(*args.shape, steps=args.steps, warmup=args.warmup)
         return
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
