@@ -344,7 +344,7 @@ head_train_wide_kernel(const __grid_constant__ CUtensorMap tmap_x,    // x [n, h
               }
               umma_commit_pair_mask(ring_empty(first + stage), pair_mask);
               // block kc / 4 of every P buffer this pair reads is free once these MMAs retire:
-              // tell the CTA that produces it (the other pair's commit completes its barrier)
+              // tell the CTA that produces it (the commits of all four pairs complete its barrier)
               if ((kc & (KC_PER_BLOCK - 1)) == KC_PER_BLOCK - 1)
                 umma_commit_pair_mask(p_empty, static_cast<uint16_t>(1u << (kc / KC_PER_BLOCK)));
             }
@@ -394,7 +394,7 @@ head_train_wide_kernel(const __grid_constant__ CUtensorMap tmap_x,    // x [n, h
       }
     }
   } else {
-    // ------------------------------- epilogue warps (every CTA) -----------------------
+    // ---------- epilogue warps (producers: every step; consumers: the drain of a unit) ----------
     const int quad = warp & 3;                  // TMEM lane quadrant of this warp
     const int hf = (warp - 4) >> 2;             // which 64 rows of the tile this warp handles
     const int vi = quad * 32 + lane;            // TMEM lane: vocabulary row in G1, h column in G2
