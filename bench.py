@@ -631,6 +631,67 @@ def run_norm_bandwidth(rows, hidden, iters=20):
     print(json.dumps(out))
 
 
+def run_weight_bandwidth(vocab, hidden, lookups, iters=20):
+    """The kernels of the shared fp16 head / embedding weight (HBM bound) on a weight larger than
+    L2: the cast-and-count pass (4 B read + 2 B written per element), the embedding lookup
+    (2 H read + 4 H written per row) and the exact fp32 rebuild (2 B + 4 B per element)."""
+    sys.path.insert(0, ROOT)
+    from esep_soup_kernels_b200.head.weight import Fp16Fixup
+
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g = torch.Generator().manual_seed(0)
+    w32 = torch.empty(vocab, hidden, device=dev)
+    for lo in range(0, vocab, 16384):
+        n = min(16384, vocab - lo)
+        w32[lo:lo + n] = (torch.randn(n, hidden, generator=g) * 0.02).to(torch.bfloat16).float().to(dev)
+    ids = torch.randint(0, vocab, (lookups,), generator=g).to(dev)
+    w16, fix = Fp16Fixup.cast(w32)
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+
+    peak = _peaks()["hbm_gbs"]
+    elems = vocab * hidden
+    out = {"metric": "shared fp16 weight kernels GB/s", "vocab": vocab, "hidden": hidden,
+           "lookups": lookups, "entries": fix.count, "rows_with_entries": fix.rows,
+           "most_in_one_row": fix.width, "table_bytes": fix.nbytes()}
+    from esep_soup_kernels_b200.head import _lib
+    from esep_soup_kernels_b200.head.op import _ptr, _stream
+    lib = _lib.load()
+    row_start = torch.empty(vocab + 1, device=dev, dtype=torch.int32)
+    stats = torch.empty(3 + (vocab + 1023) // 1024, device=dev, dtype=torch.int64)
+    w16b = torch.empty_like(w16)
+
+    def scan():       # the two passes of the set-up on their own (no host read in between)
+        _lib.check("esep_weight_fixup_scan", lib.esep_weight_fixup_scan(
+            _ptr(w32), _ptr(w16b), 1, vocab, hidden, _ptr(row_start), _ptr(stats), _stream(dev)))
+
+    def fill():
+        _lib.check("esep_weight_fixup_fill", lib.esep_weight_fixup_fill(
+            _ptr(w32), _ptr(w16), vocab, hidden, _ptr(fix.row_start), _ptr(fix.flat_idx),
+            _ptr(fix.flat_val), _stream(dev)))
+
+    for name, nbytes, fn in (
+            ("cast_and_count", 6 * elems, scan),
+            ("fill", 6 * hidden * fix.rows, fill),
+            ("set_up_whole", 6 * elems + 6 * hidden * fix.rows, lambda: Fp16Fixup.cast(w32)),
+            ("embed", 6 * hidden * lookups, lambda: fix.embed(w16, ids)),
+            ("exact_weight", 6 * elems, lambda: fix.exact_weight(w16))):
+        ms = timed(fn)
+        out[name] = {"us": ms * 1e3, "algorithmic_mb": nbytes / 1e6, "gbs": nbytes / ms / 1e6,
+                     "frac_of_measured_hbm": nbytes / ms / 1e6 / peak}
+    print(json.dumps(out))
+
+
 def run_shape(rows, hidden, vocab, steps, warmup):
     """fused_linear_ce + backward on a synthetic bf16 problem of the given shape on one GPU (e.g.
     one vocabulary shard of the 7B configuration: 32768 3584 19008): ms per step with a CUDA
@@ -684,6 +745,8 @@ def main():
                          "profiler captures); the line then lacks sustained / cpu_baseline")
     ap.add_argument("--norm-bandwidth", nargs=2, type=int, metavar=("ROWS", "HIDDEN"),
                     help="instead of the head: time the final-norm kernels on ROWS x HIDDEN")
+    ap.add_argument("--weight-bandwidth", nargs=3, type=int, metavar=("VOCAB", "HIDDEN", "LOOKUPS"),
+                    help="instead of the head: time the kernels of the shared fp16 weight format")
     ap.add_argument("--shape", nargs=3, type=int, metavar=("ROWS", "HIDDEN", "VOCAB"),
                     help="instead of configuration 2: time the head step (bf16) on this shape")
     args = ap.parse_args()
@@ -692,6 +755,9 @@ def main():
         return
     if args.shape:
         run_shape(*args.shape, steps=args.steps, warmup=args.warmup)
+        return
+    if args.weight_bandwidth:
+        run_weight_bandwidth(*args.weight_bandwidth)
         return
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":

@@ -19,6 +19,7 @@
 #include "head_step.cuh"
 #include "head_train.cuh"
 #include "head_train_wide.cuh"
+#include "head_weight.cuh"
 
 using namespace esep;
 
@@ -1409,6 +1410,110 @@ int esep_head_grad_scale(const float* dx, const float* grad_loss, int64_t count,
   else head_grad_scale_kernel<2><<<grid, 256, 0, s>>>(src, grad_loss, n4, out);
   if (cudaGetLastError() != cudaSuccess) return ESEP_ERR_CUDA;
   g_launches.fetch_add(1);
+  return ESEP_OK;
+}
+
+// ---- the shared fp16 weight format (head_weight.cuh) ------------------------------------------
+int esep_weight_fixup_scan(const float* w32, void* w16, int cast, int64_t v, int64_t h,
+                           int32_t* row_start, int64_t* stats, void* stream) {
+  if (w32 == nullptr || w16 == nullptr || row_start == nullptr || stats == nullptr)
+    return ESEP_ERR_BAD_ARG;
+  if (v <= 0 || h <= 0 || h % 8 != 0 || v >= (1LL << 31) - 1 || h > (1 << 20))
+    return ESEP_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(w32) & 15u) || (reinterpret_cast<uintptr_t>(w16) & 15u))
+    return ESEP_ERR_ALIGNMENT;
+  const DeviceInfo* d = nullptr;
+  const int st = current_device_info(&d);
+  if (st != ESEP_OK) return st;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const unsigned row_blocks = static_cast<unsigned>((v + 1023) / 1024);
+  long long* st64 = reinterpret_cast<long long*>(stats);
+  if (cudaMemsetAsync(st64, 0, (3 + static_cast<size_t>(row_blocks)) * sizeof(long long), s) !=
+      cudaSuccess)
+    return ESEP_ERR_CUDA;
+  const unsigned rows_grid = static_cast<unsigned>(v);
+  if (cast)
+    head_w16_scan_kernel<true><<<rows_grid, 128, 0, s>>>(w32, static_cast<__half*>(w16),
+                                                         static_cast<int>(v), static_cast<int>(h),
+                                                         row_start, st64);
+  else
+    head_w16_scan_kernel<false><<<rows_grid, 128, 0, s>>>(w32, static_cast<__half*>(w16),
+                                                          static_cast<int>(v), static_cast<int>(h),
+                                                          row_start, st64);
+  if (cudaGetLastError() != cudaSuccess) return ESEP_ERR_CUDA;
+  head_w16_offsets_kernel<<<row_blocks, 1024, 0, s>>>(row_start, static_cast<int>(v), st64);
+  if (cudaGetLastError() != cudaSuccess) return ESEP_ERR_CUDA;
+  g_launches.fetch_add(2);
+  return ESEP_OK;
+}
+
+int esep_weight_fixup_fill(const float* w32, const void* w16, int64_t v, int64_t h,
+                           const int32_t* row_start, int64_t* flat_idx, float* flat_val,
+                           void* stream) {
+  if (w32 == nullptr || w16 == nullptr || row_start == nullptr || flat_idx == nullptr ||
+      flat_val == nullptr)
+    return ESEP_ERR_BAD_ARG;
+  if (v <= 0 || h <= 0 || h % 8 != 0 || v >= (1LL << 31) - 1 || h > (1 << 20))
+    return ESEP_ERR_BAD_ARG;
+  const DeviceInfo* d = nullptr;
+  const int st = current_device_info(&d);
+  if (st != ESEP_OK) return st;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  head_w16_fill_kernel<<<static_cast<unsigned>(v), 128, 0, s>>>(w32, static_cast<const __half*>(w16),
+                                            static_cast<int>(v), static_cast<int>(h), row_start,
+                                            reinterpret_cast<long long*>(flat_idx), flat_val);
+  if (cudaGetLastError() != cudaSuccess) return ESEP_ERR_CUDA;
+  g_launches.fetch_add(1);
+  return ESEP_OK;
+}
+
+int esep_embed_rows(const void* w16, const int64_t* ids, int64_t n, int64_t v, int64_t h,
+                    const int32_t* row_start, const int64_t* flat_idx, const float* flat_val,
+                    float* out, int* status, void* stream) {
+  if (ids == nullptr || out == nullptr || n < 0 || n > (1LL << 30)) return ESEP_ERR_BAD_ARG;
+  if (v <= 0 || h <= 0 || h % 8 != 0 || v >= (1LL << 31) - 1 || h > (1 << 20))
+    return ESEP_ERR_BAD_ARG;
+  if (row_start != nullptr && (flat_idx == nullptr || flat_val == nullptr)) return ESEP_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(w16) & 15u) || (reinterpret_cast<uintptr_t>(out) & 15u))
+    return ESEP_ERR_ALIGNMENT;
+  if (n == 0 || (w16 == nullptr && row_start == nullptr)) return ESEP_OK;
+  const DeviceInfo* d = nullptr;
+  const int st = current_device_info(&d);
+  if (st != ESEP_OK) return st;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  head_embed_rows_kernel<<<static_cast<unsigned>(n), 128, 0, s>>>(
+      static_cast<const __half*>(w16), reinterpret_cast<const long long*>(ids),
+      static_cast<int>(v), static_cast<int>(h), row_start,
+      reinterpret_cast<const long long*>(flat_idx), flat_val, out, status);
+  if (cudaGetLastError() != cudaSuccess) return ESEP_ERR_CUDA;
+  g_launches.fetch_add(1);
+  return ESEP_OK;
+}
+
+int esep_weight_exact(const void* w16, int64_t v, int64_t h, int64_t count,
+                      const int64_t* flat_idx, const float* flat_val, float* out, void* stream) {
+  if (w16 == nullptr || out == nullptr || count < 0) return ESEP_ERR_BAD_ARG;
+  if (v <= 0 || h <= 0 || h % 8 != 0 || v >= (1LL << 31) - 1 || h > (1 << 20))
+    return ESEP_ERR_BAD_ARG;
+  if (count > 0 && (flat_idx == nullptr || flat_val == nullptr)) return ESEP_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(w16) & 15u) || (reinterpret_cast<uintptr_t>(out) & 15u))
+    return ESEP_ERR_ALIGNMENT;
+  const DeviceInfo* d = nullptr;
+  const int st = current_device_info(&d);
+  if (st != ESEP_OK) return st;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const size_t n8 = static_cast<size_t>(v) * h / 8;
+  if ((n8 + 1023) / 1024 > 0x7fffffffull) return ESEP_ERR_BAD_ARG;
+  const unsigned grid = static_cast<unsigned>((n8 + 1023) / 1024);
+  head_w16_upcast_kernel<<<grid, 256, 0, s>>>(static_cast<const __half*>(w16), n8, out);
+  if (cudaGetLastError() != cudaSuccess) return ESEP_ERR_CUDA;
+  g_launches.fetch_add(1);
+  if (count > 0) {
+    head_w16_restore_kernel<<<static_cast<unsigned>((count + 255) / 256), 256, 0, s>>>(
+        reinterpret_cast<const long long*>(flat_idx), flat_val, count, out);
+    if (cudaGetLastError() != cudaSuccess) return ESEP_ERR_CUDA;
+    g_launches.fetch_add(1);
+  }
   return ESEP_OK;
 }
 

@@ -36,6 +36,7 @@ enum : int {
   DEV_TIMEOUT_PRODUCER = 101,
   DEV_TIMEOUT_MMA = 102,
   DEV_TIMEOUT_EPILOGUE = 103,
+  DEV_BAD_INDEX = 301,   // an embedding id outside the vocabulary (head_embed_rows_kernel)
 };
 
 struct FwdParams {

@@ -23,6 +23,7 @@ DTYPE_F32 = 2
 RECORD_FIELDS = 5
 METRIC_SCALARS = 4
 STEP_SCALARS = 8
+DEV_BAD_INDEX = 301       # device status: an embedding id outside the vocabulary
 
 
 class Caps(ctypes.Structure):
@@ -86,6 +87,10 @@ SIGNATURES = {
     "esep_head_norm_forward": (_INT, [_P, _P, _P, _I64, _I64, ctypes.c_float, _INT, _P, _P, _P,
                                       _P]),
     "esep_head_norm_backward": (_INT, [_P, _P, _P, _P, _P, _I64, _I64, _INT, _P, _P, _P]),
+    "esep_weight_fixup_scan": (_INT, [_P, _P, _INT, _I64, _I64, _P, _P, _P]),
+    "esep_weight_fixup_fill": (_INT, [_P, _P, _I64, _I64, _P, _P, _P, _P]),
+    "esep_embed_rows": (_INT, [_P, _P, _I64, _I64, _I64, _P, _P, _P, _P, _P, _P]),
+    "esep_weight_exact": (_INT, [_P, _I64, _I64, _I64, _P, _P, _P, _P]),
 }
 
 _lib = None

@@ -255,6 +255,47 @@ int esep_head_vp_combine(const float* records, int n_records, int my_record,
 int esep_head_grad_scale(const float* dx, const float* grad_loss, int64_t count, int out_dtype,
                          void* out, void* stream);
 
+/* ---- the head weight's storage format: one fp16 tensor shared with the embedding ---------------
+ *
+ * The reference replaces the frozen fp32 tied embed / lm_head weight by ONE fp16 tensor and keeps,
+ * for the embedding lookup, a table of the elements that do not survive fp32 -> fp16 -> fp32
+ * (solution/head/patch.py:105-123 for the why, :133-215 _Fp16Fixup, :217-226 _embedding_forward16).
+ * Here the table is three device arrays in compressed-row form, built in two calls with one host
+ * read of the entry count between them (set-up time, as the reference's own .numel()):
+ *
+ *   row_start int32 [v + 1]   entries of row r are [row_start[r], row_start[r + 1])
+ *   flat_idx  int64 [count]   r * h + column of each entry, ascending (= patch.py:145-148)
+ *   flat_val  fp32  [count]   the exact value
+ */
+
+/* Pass 1. cast != 0: writes w16 = fp16(w32) (round to nearest even) and counts; cast == 0: w16 is
+ * the caller's fp16 tensor and is only compared. Leaves row_start complete and
+ * stats[0 .. 3) = {entries, rows with entries, most entries in one row}; stats is device memory,
+ * int64 [3 + (v + 1023) / 1024] (the tail is scratch: entries per block of 1024 rows).
+ * Replaces: `w32.to(torch.float16)` + the compare / nonzero loop of patch.py:141-150. */
+int esep_weight_fixup_scan(const float* w32, void* w16, int cast, int64_t v, int64_t h,
+                           int32_t* row_start, int64_t* stats, void* stream);
+
+/* Pass 2: fills flat_idx / flat_val (each with room for stats[0] entries). */
+int esep_weight_fixup_fill(const float* w32, const void* w16, int64_t v, int64_t h,
+                           const int32_t* row_start, int64_t* flat_idx, float* flat_val,
+                           void* stream);
+
+/* out [n, h] fp32 = the ORIGINAL fp32 rows ids[0 .. n) bit for bit: gather of fp16 rows, upcast
+ * and the rows' entries in one kernel. w16 == NULL: out already holds the upcast rows, only the
+ * entries are written (= _Fp16Fixup.apply_rows, patch.py:201-210). row_start == NULL: a weight
+ * without entries (= _Fp16Fixup.exact, patch.py:177-194). An id outside [0, v) yields a zero row
+ * and sets *status (may be NULL) to 301; nothing is read out of bounds.
+ * Replaces: _embedding_forward16 (F.embedding + .to(fp32) + gather / where / scatter_). */
+int esep_embed_rows(const void* w16, const int64_t* ids, int64_t n, int64_t v, int64_t h,
+                    const int32_t* row_start, const int64_t* flat_idx, const float* flat_val,
+                    float* out, int* status, void* stream);
+
+/* out [v, h] fp32 = the original fp32 weight bit for bit (= _Fp16Fixup.exact_weight,
+ * patch.py:212-215: the lm_head outside fp16 autocast). */
+int esep_weight_exact(const void* w16, int64_t v, int64_t h, int64_t count,
+                      const int64_t* flat_idx, const float* flat_val, float* out, void* stream);
+
 /* Counters: out[0] = per-device initialisations performed so far (function attributes,
  * occupancy queries), out[1] = tensor maps encoded so far (maps are cached by address and
  * shape) - a warmed-up process that repeats a call sees neither number move; out[2] (n >= 3) =

@@ -16,7 +16,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 def _declared_symbols():
     text = open(os.path.join(ROOT, "include", "esep_head.h")).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(esep_head_[a-z_]+)\s*\(", text)))
+    return sorted(set(re.findall(r"\b(esep_(?:head|weight|embed)_[a-z_]+)\s*\(", text)))
 
 
 def test_library_exports_every_declared_symbol():

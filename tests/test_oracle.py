@@ -12,7 +12,7 @@ import torch
 from oracle import head_oracle as ho
 
 GOLDEN = sorted(p for p in glob.glob(os.path.join(os.path.dirname(__file__), "golden", "*.npz"))
-                if not os.path.basename(p).startswith("final_norm"))   # head cases only
+                if not os.path.basename(p).startswith(("final_norm", "fp16_fixup")))   # head cases only
 
 
 def _load(path):
