@@ -692,14 +692,15 @@ def run_weight_bandwidth(vocab, hidden, lookups, iters=20):
     print(json.dumps(out))
 
 
-def run_shape(rows, hidden, vocab, steps, warmup):
+def run_shape(rows, hidden, vocab, steps, warmup, path=0):
     """fused_linear_ce + backward on a synthetic bf16 problem of the given shape on one GPU (e.g.
     one vocabulary shard of the 7B configuration: 32768 3584 19008): ms per step with a CUDA
     event pair, algorithmic TFLOP/s (4 H V per row) and its share of the measured tensor peak.
     A profiler capture of a kernel at another hidden size uses this with few rows."""
     sys.path.insert(0, ROOT)
-    from esep_soup_kernels_b200.head import fused_linear_ce, last_device_status
+    from esep_soup_kernels_b200.head import _lib, fused_linear_ce, last_device_status
 
+    _lib.load().esep_head_set_training_path(int(path))
     dev = torch.device("cuda", torch.cuda.current_device())
     g = torch.Generator().manual_seed(0)
     x = torch.randn(rows, hidden, generator=g).to(torch.bfloat16).to(dev)
@@ -728,7 +729,7 @@ def run_shape(rows, hidden, vocab, steps, warmup):
     ms = e0.elapsed_time(e1) / steps
     tf = 4.0 * hidden * vocab * rows / (ms * 1e-3) / 1e12
     print(json.dumps({"metric": "head step on a given shape", "rows": rows, "hidden": hidden,
-                      "vocab": vocab, "dtype": "bfloat16", "steps": steps, "ms_per_step": ms,
+                      "vocab": vocab, "dtype": "bfloat16", "path": path, "steps": steps, "ms_per_step": ms,
                       "rows_s": rows / (ms * 1e-3), "algorithmic_tflops": tf,
                       "frac_of_measured_tensor_peak": tf / _peaks()["tflops"],
                       "loss": float(loss.detach()), "device_status": last_device_status()}))
@@ -747,6 +748,9 @@ def main():
                     help="instead of the head: time the final-norm kernels on ROWS x HIDDEN")
     ap.add_argument("--weight-bandwidth", nargs=3, type=int, metavar=("VOCAB", "HIDDEN", "LOOKUPS"),
                     help="instead of the head: time the kernels of the shared fp16 weight format")
+    ap.add_argument("--path", type=int, default=0, choices=[0, 1, 2],
+                    help="with --shape: training path (esep_head_set_training_path): 0 auto, "
+                         "1 single pass, 2 two sweeps over stored logits")
     ap.add_argument("--shape", nargs=3, type=int, metavar=("ROWS", "HIDDEN", "VOCAB"),
                     help="instead of configuration 2: time the head step (bf16) on this shape")
     args = ap.parse_args()
@@ -754,7 +758,7 @@ def main():
         run_norm_bandwidth(*args.norm_bandwidth)
         return
     if args.shape:
-        run_shape(*args.shape, steps=args.steps, warmup=args.warmup)
+        run_shape(*args.shape, steps=args.steps, warmup=args.warmup, path=args.path)
         return
     if args.weight_bandwidth:
         run_weight_bandwidth(*args.weight_bandwidth)

@@ -14,6 +14,7 @@
 
 #include "head_aux.cuh"
 #include "head_bwd.cuh"
+#include "head_dx.cuh"
 #include "head_fwd.cuh"
 #include "head_norm.cuh"
 #include "head_step.cuh"
@@ -32,6 +33,7 @@ constexpr size_t kAlign = 256;
 struct DeviceInfo {
   int cc_major = 0, cc_minor = 0, sm_count = 0, max_clusters_bwd = 0, max_pairs_fwd = 0;
   int max_clusters_wide = 0;   // resident 8-CTA clusters of head_train_wide_kernel (0: not available)
+  int max_pairs_dx = 0;        // resident CTA pairs of head_dx_kernel (0: not available)
   int init_status = ESEP_ERR_CUDA;
 };
 
@@ -45,6 +47,9 @@ PFN_cuTensorMapEncodeTiled g_encode = nullptr;
 std::atomic<long long> g_init_calls{0};   // completed per-device initialisations (test aid)
 std::atomic<long long> g_launches{0};     // kernels this library has launched (all entry points)
 std::atomic<long long> g_wide_launches{0};   // of head_train_wide_kernel
+std::atomic<long long> g_dx_launches{0};     // of head_dx_kernel
+std::atomic<int> g_training_path{0};          // esep_head_set_training_path
+constexpr size_t kMaxStoredLogitsBytes = static_cast<size_t>(48) << 30;
 
 size_t align_up(size_t x) { return (x + kAlign - 1) / kAlign * kAlign; }
 
@@ -157,6 +162,32 @@ bool init_device(int device) {
         cudaOccupancyMaxActiveClusters(&ncl, head_train_wide_kernel<0>, &cfg) == cudaSuccess &&
         ncl > 0)
       d.max_clusters_wide = std::min(ncl, d.sm_count / trnw::CLW);
+  }
+  if (ok) {
+    // CTA pairs of the dHidden-from-stored-logits kernel, and the attributes of the storing sweep.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(d.sm_count / 2 * 2));
+    cfg.blockDim = dim3(dxk::THREADS);
+    cfg.dynamicSmemBytes = dxk::SMEM_BYTES;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int npairs = 0;
+    if (cudaFuncSetAttribute(head_dx_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             dxk::SMEM_BYTES) == cudaSuccess &&
+        cudaFuncSetAttribute(head_dx_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             dxk::SMEM_BYTES) == cudaSuccess &&
+        cudaFuncSetAttribute(head_fwd_kernel<0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             fwd::SMEM_BYTES) == cudaSuccess &&
+        cudaFuncSetAttribute(head_fwd_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             fwd::SMEM_BYTES) == cudaSuccess &&
+        cudaOccupancyMaxActiveClusters(&npairs, head_dx_kernel<0>, &cfg) == cudaSuccess &&
+        npairs > 0)
+      d.max_pairs_dx = std::min(npairs, d.sm_count / 2);
   }
   cudaGetLastError();
   cudaSetDevice(prev);
@@ -862,6 +893,9 @@ struct StepLayout {
   int nhb_a, nhb_b;    // wide: accumulator blocks per producer / consumer CTA
   int rows_nhb;        // accumulator blocks per quarter of a pass, as the row-finish kernel sees it
   int pass_w;          // columns per pass = row stride of the partial dHidden pieces
+  bool stored;         // two sweeps: forward sweep that stores the logits, then head_dx_kernel
+  size_t zpitch;       // elements per row of the stored logits
+  size_t z_off, c2_off, partg_off, pieces_off;
   int part_cap;        // rows of the forward partial arrays
   size_t base_bytes;
   size_t record_off, st_off, st_stride, lo_off, lo_stride, dxpart_off, xc_off, tgtc_off, tgto_off,
@@ -898,6 +932,19 @@ int step_layout(int64_t m, int64_t h, int64_t v, bool need_grad, const DeviceInf
     t->ncl = static_cast<int>(
         std::min<int64_t>(d->max_clusters_wide, n_tp * pl.bwd_total_steps));
   }
+  t->stored = false;
+  t->zpitch = static_cast<size_t>(pl.fwd_vocab_tiles) * 256;
+  {
+    const int path = g_training_path.load();
+    const size_t zbytes = static_cast<size_t>(m) * t->zpitch * 2;
+    // Measured on B200: where one 4-CTA cluster holds the whole dHidden accumulator (H <= 1536) the
+    // single pass is the faster one (3.55 against 3.72 ms at 4 340 x 1536 x 151 936); above it the
+    // two sweeps are (hidden 3584, 32 768 x 19 008: 10.1 against 13.5 ms on 8-CTA clusters).
+    const bool wanted = path == 2 || (path == 0 && pl.bwd_passes > 1);
+    if (need_grad && wanted && d->max_pairs_dx > 0 && h % 64 == 0 &&
+        zbytes <= kMaxStoredLogitsBytes)
+      t->stored = true;
+  }
   const size_t mr = static_cast<size_t>(div_up(m, 256)) * 256;
   t->part_cap = static_cast<int>(std::min<size_t>(mr + static_cast<size_t>(4) * 256 * d->max_pairs_fwd,
                                                   static_cast<size_t>(1) << 30));
@@ -921,8 +968,8 @@ int step_layout(int64_t m, int64_t h, int64_t v, bool need_grad, const DeviceInf
   t->record_off = off;
   t->st_off = t->lo_off = t->dxpart_off = t->dxc_off = t->fb_off = t->fbam_off = t->floss_off = off;
   t->st_stride = t->lo_stride = t->fb_stride = 0;
-  if (need_grad) {
-    t->record_off = take(static_cast<size_t>(ESEP_RECORD_FIELDS) * m * f4);
+  if (need_grad) t->record_off = take(static_cast<size_t>(ESEP_RECORD_FIELDS) * m * f4);
+  if (need_grad && !t->stored) {
     t->st_stride = align_up(static_cast<size_t>(16) * m * f4);
     t->st_off = take(4 * t->st_stride);
     // a left-over pair is cut into at most ncl / rem_tp runs: rem_tp * rem_splits <= ncl
@@ -934,6 +981,15 @@ int step_layout(int64_t m, int64_t h, int64_t v, bool need_grad, const DeviceInf
     t->fb_off = take(5 * t->fb_stride);
     t->fbam_off = take(static_cast<size_t>(m) * 8);
     t->floss_off = take(kAlign);
+  }
+  t->z_off = t->c2_off = t->partg_off = t->pieces_off = off;
+  if (t->stored) {
+    t->z_off = take(static_cast<size_t>(m) * t->zpitch * 2);
+    t->c2_off = take(2 * align_up(static_cast<size_t>(m) * f4));   // kexp, rscale
+    t->partg_off = take(5 * t->part_stride);
+    t->pieces_off = take(static_cast<size_t>(dx_max_runs(static_cast<int>(m), static_cast<int>(h),
+                                                         static_cast<int>(v), d->max_pairs_dx)) *
+                         dxk::ROWS * dxk::SLICE * f4);
   }
   t->total = off;
   return ESEP_OK;
@@ -1073,6 +1129,77 @@ int step_impl(const StepArgs& a) {
                                    a.workspace, t.base_bytes, a.stream);
     if (st != ESEP_OK) return st;
 
+  }
+  const unsigned fwd_grid = static_cast<unsigned>(2 * d->max_pairs_fwd);
+  float* part_g = reinterpret_cast<float*>(ws + t.partg_off);
+  const size_t psg = t.part_stride / sizeof(float);
+  if (need_grad && t.stored) {
+    // 4a. forward sweep over the compact rows [0, n_sweep) that keeps logit - m_ref as fp16
+    CUtensorMap tx, tw;
+    if (make_tmap(&tx, xc, a.dtype, a.m, a.h, fwd::BK, fwd::BM) != ESEP_OK) return ESEP_ERR_CUDA;
+    if (make_tmap(&tw, a.w, a.dtype, a.v, a.h, fwd::BK, fwd::BN / 2) != ESEP_OK)
+      return ESEP_ERR_CUDA;
+    FwdParams g = {};
+    g.n = m;
+    g.h = h;
+    g.v = v;
+    g.n_row_tiles = pl.fwd_row_tiles;
+    g.n_row_pairs = div_up(pl.fwd_row_tiles, 2);
+    g.n_vtiles = pl.fwd_vocab_tiles;
+    g.tiles_per_unit = pl.fwd_tiles_per_unit;
+    g.n_splits = pl.fwd_splits;
+    g.vocab_offset = 0;
+    g.target = tgt_c;
+    g.pm = part_g;
+    g.ps = part_g + psg;
+    g.pt = part_g + 2 * psg;
+    g.ptz = part_g + 3 * psg;
+    g.pidx = reinterpret_cast<int*>(part_g + 4 * psg);
+    g.status = status;
+    g.gate = nullptr;
+    g.row_range = counts + CNT_ZERO;   // {0, n_sweep}
+    g.part_cap = t.part_cap;
+    g.zbuf = reinterpret_cast<__half*>(ws + t.z_off);
+    g.zpitch = static_cast<long long>(t.zpitch);
+    g.m_ref = record;
+    st = a.dtype == ESEP_DTYPE_F16
+             ? launch_cluster(head_fwd_kernel<0, true>, fwd_grid, fwd::THREADS, fwd::SMEM_BYTES, 2,
+                              s, tx, tw, g)
+             : launch_cluster(head_fwd_kernel<1, true>, fwd_grid, fwd::THREADS, fwd::SMEM_BYTES, 2,
+                              s, tx, tw, g);
+    if (st != ESEP_OK) return st;
+    // 4b. per-row constant of the softmax weights, 4c. dHidden from the stored logits
+    float* kexp = reinterpret_cast<float*>(ws + t.c2_off);
+    float* rscale = reinterpret_cast<float*>(ws + t.c2_off + align_up(static_cast<size_t>(m) * sizeof(float)));
+    const unsigned rc_grid = static_cast<unsigned>(div_up(m, 128));
+    head_dx_rowconst_kernel<<<rc_grid, 128, 0, s>>>(m, counts + CNT_SWEEP, pl.fwd_vocab_tiles,
+                                                    static_cast<int>(fwd_grid / 2), t.part_cap, g.pm,
+                                                    g.ps, g.ptz, tgt_c, v, record, kexp, rscale);
+    if (cudaGetLastError() != cudaSuccess) return ESEP_ERR_CUDA;
+    g_launches.fetch_add(1);
+    CUtensorMap tw3;
+    if (make_tmap_w3(&tw3, a.w, a.dtype, a.v, a.h, dxk::KV, 4) != ESEP_OK) return ESEP_ERR_CUDA;
+    DxParams dp = {};
+    dp.n = m;
+    dp.h = h;
+    dp.v = v;
+    dp.n_dev = counts + CNT_SWEEP;
+    dp.z = g.zbuf;
+    dp.zpitch = g.zpitch;
+    dp.kexp = kexp;
+    dp.target = tgt_c;
+    dp.pieces = reinterpret_cast<float*>(ws + t.pieces_off);
+    dp.status = status;
+    const unsigned dx_grid = static_cast<unsigned>(2 * d->max_pairs_dx);
+    st = a.dtype == ESEP_DTYPE_F16
+             ? launch_cluster(head_dx_kernel<0>, dx_grid, dxk::THREADS, dxk::SMEM_BYTES, 2, s, tw3,
+                              dp)
+             : launch_cluster(head_dx_kernel<1>, dx_grid, dxk::THREADS, dxk::SMEM_BYTES, 2, s, tw3,
+                              dp);
+    if (st != ESEP_OK) return st;
+    g_dx_launches.fetch_add(1);
+  }
+  if (need_grad && !t.stored) {
     // 4. the training sweep over the compact rows [0, n_sweep)
     CUtensorMap tx, tw1, tw2, tw2b;
     if (make_tmap(&tx, xc, a.dtype, a.m, a.h, bwd::BK, 64) != ESEP_OK) return ESEP_ERR_CUDA;
@@ -1148,7 +1275,6 @@ int step_impl(const StepArgs& a) {
   }
 
   // 5. forward sweep over the compact rows [n_sweep, n_sel): statistics only
-  const unsigned fwd_grid = static_cast<unsigned>(2 * d->max_pairs_fwd);
   FwdParams f = {};
   {
     CUtensorMap tx, tw;
@@ -1186,7 +1312,7 @@ int step_impl(const StepArgs& a) {
   float* fb = reinterpret_cast<float*>(ws + t.fb_off);
   const size_t fbs = t.fb_stride / sizeof(float);
   long long* fb_amax = reinterpret_cast<long long*>(ws + t.fbam_off);
-  if (need_grad) {
+  if (need_grad && !t.stored) {
     // 6. guarded second attempt on the compact rows: the two-kernel path, enqueued behind the
     //    overflow flag. Its kernels return at once unless a row overflowed in the sweep; if one
     //    did, they leave per-row results and final dHidden rows in compact order.
@@ -1235,6 +1361,15 @@ int step_impl(const StepArgs& a) {
   r.amax = reinterpret_cast<long long*>(a.argmax);
   r.top = a.top_logit;
   r.dx = need_grad ? a.dx : nullptr;
+  r.stored = (need_grad && t.stored) ? 1 : 0;
+  r.dx_pairs = d->max_pairs_dx;
+  r.g_rscale = reinterpret_cast<const float*>(ws + t.c2_off + align_up(static_cast<size_t>(a.m) * sizeof(float)));
+  r.g_pm = part_g;
+  r.g_ps = part_g + psg;
+  r.g_pt = part_g + 2 * psg;
+  r.g_ptz = part_g + 3 * psg;
+  r.g_pidx = reinterpret_cast<const int*>(part_g + 4 * psg);
+  r.pieces = reinterpret_cast<const float*>(ws + t.pieces_off);
   if (a.dtype == ESEP_DTYPE_F16)
     head_step_rows_kernel<0><<<static_cast<unsigned>(m), 128, 0, s>>>(r);
   else
@@ -1517,12 +1652,18 @@ int esep_weight_exact(const void* w16, int64_t v, int64_t h, int64_t count,
   return ESEP_OK;
 }
 
+int esep_head_set_training_path(int path) {
+  if (path < 0 || path > 2) return ESEP_ERR_BAD_ARG;
+  return g_training_path.exchange(path);
+}
+
 int esep_head_debug_counters(long long* out, int n) {
   if (out == nullptr || n < 2) return ESEP_ERR_BAD_ARG;
   out[0] = g_init_calls.load();
   out[1] = g_tmap_encodes.load();
   if (n >= 3) out[2] = g_launches.load();
   if (n >= 4) out[3] = g_wide_launches.load();
+  if (n >= 5) out[4] = g_dx_launches.load();
   return ESEP_OK;
 }
 

@@ -22,6 +22,8 @@
 // of tile k.
 #pragma once
 
+#include <cuda_fp16.h>
+
 #include "sm100_ptx.cuh"
 
 namespace esep {
@@ -63,6 +65,13 @@ struct FwdParams {
   // [split][row - row_range[0]] with a stride of fwd_split_rows().stride.
   const int* row_range;
   int part_cap;        // rows the partial arrays hold (splits * stride never exceeds it)
+  // kStore launches only (the sweep that keeps the logits for the dHidden kernel, head_dx.cuh):
+  // zbuf[row - row_range[0]][vocab] = fp16((logit - m_ref[row]) * log2 e) with `zpitch` elements per row
+  // (a multiple of 256, so that whole tiles can be stored); the row sums then leave the
+  // target's own entry out, as the training sweeps do (it is added in fp32 by the row finish).
+  __half* zbuf;
+  long long zpitch;
+  const float* m_ref;
 };
 
 // Work split of the forward sweep for a row count that is only known on the device: the
@@ -127,6 +136,7 @@ struct RowState {
   int idx;
 };
 
+template <bool kExclTarget = false>
 __device__ __forceinline__ void fold_chunk(RowState& st, const uint32_t (&r)[32], int col0,
                                            int nvalid, int tgt_local) {
   float z[32];
@@ -155,12 +165,17 @@ __device__ __forceinline__ void fold_chunk(RowState& st, const uint32_t (&r)[32]
     st.ml2 = cm * LOG2E;
   }
   float cs0 = 0.f, cs1 = 0.f, ct0 = 0.f, ct1 = 0.f;
+  const unsigned tl = static_cast<unsigned>(tgt_local - col0);
 #pragma unroll
   for (int j = 0; j < 32; j += 2) {
     const float d0 = fmaf(z[j], LOG2E, -st.ml2);
     const float d1 = fmaf(z[j + 1], LOG2E, -st.ml2);
-    const float e0 = ex2_approx(d0);
-    const float e1 = ex2_approx(d1);
+    float e0 = ex2_approx(d0);
+    float e1 = ex2_approx(d1);
+    if (kExclTarget) {   // the target's entry stays out of the sums
+      if (static_cast<unsigned>(j) == tl) e0 = 0.f;
+      if (static_cast<unsigned>(j + 1) == tl) e1 = 0.f;
+    }
     cs0 += e0;
     cs1 += e1;
     ct0 = fmaf(e0, d0, ct0);
@@ -168,7 +183,6 @@ __device__ __forceinline__ void fold_chunk(RowState& st, const uint32_t (&r)[32]
   }
   st.s += cs0 + cs1;
   st.t2 += ct0 + ct1;
-  const unsigned tl = static_cast<unsigned>(tgt_local - col0);
   if (tl < 32u) {
 #pragma unroll
     for (int j = 0; j < 32; ++j)
@@ -176,7 +190,7 @@ __device__ __forceinline__ void fold_chunk(RowState& st, const uint32_t (&r)[32]
   }
 }
 
-template <int kFmt>  // 0 = fp16, 1 = bf16
+template <int kFmt, bool kStore = false>  // kFmt: 0 = fp16, 1 = bf16
 __global__ void __launch_bounds__(fwd::THREADS, 1)
 head_fwd_kernel(const __grid_constant__ CUtensorMap tmap_x,
                 const __grid_constant__ CUtensorMap tmap_w, const FwdParams p) {
@@ -340,9 +354,15 @@ head_fwd_kernel(const __grid_constant__ CUtensorMap tmap_x,
       const int vt1 = min(vt0 + tiles_per_unit, p.n_vtiles);
       const int row = row0 + rt * BM + row_in_tile;
       int tgt_local = -1;
+      float mref = 0.f;
+      __half* zrow = nullptr;
       if (row < row_end) {
         const long long tg = p.target[row] - p.vocab_offset;
         if (tg >= 0 && tg < p.v) tgt_local = static_cast<int>(tg);
+        if (kStore) {
+          mref = p.m_ref[row];
+          zrow = p.zbuf + static_cast<size_t>(row - row0) * p.zpitch;
+        }
       }
       RowState st;
       st.m = NEG_BIG;
@@ -365,7 +385,24 @@ head_fwd_kernel(const __grid_constant__ CUtensorMap tmap_x,
           tmem_ld32(taddr + c * 32, r);
           tmem_ld_wait();
           const int nvalid = tile_valid - c * 32;
-          if (nvalid > 0) fold_chunk(st, r, v0 + c * 32, nvalid, tgt_local);
+          if (kStore && zrow != nullptr) {
+            // 32 logits of this row, relative to its reference maximum and in units of ln 2, as 64
+            // bytes of fp16 (the dHidden kernel's 2^x takes them as they are)
+            uint4* dst = reinterpret_cast<uint4*>(zrow + v0 + c * 32);
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              uint32_t hw[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const __half2 hv =
+                    __floats2half2_rn((__uint_as_float(r[g * 8 + 2 * e]) - mref) * LOG2E,
+                                      (__uint_as_float(r[g * 8 + 2 * e + 1]) - mref) * LOG2E);
+                hw[e] = *reinterpret_cast<const uint32_t*>(&hv);
+              }
+              dst[g] = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+            }
+          }
+          if (nvalid > 0) fold_chunk<kStore>(st, r, v0 + c * 32, nvalid, tgt_local);
         }
         tc_fence_before();
         __syncwarp();

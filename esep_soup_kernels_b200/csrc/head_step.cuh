@@ -10,6 +10,7 @@
 //                                   cast, scatter of per-row CE / entropy back to [B, T], counts
 #pragma once
 
+#include "head_dx.cuh"
 #include "head_train.cuh"
 
 namespace esep {
@@ -19,7 +20,7 @@ namespace esep {
 //   [1] n_sel    compact rows [n_sweep, n_sel) go through the forward sweep only
 //   [2] n_live   rows with a loss term and a non-zero weight
 //   [3] unused
-enum : int { CNT_SWEEP = 0, CNT_SEL = 1, CNT_LIVE = 2 };
+enum : int { CNT_SWEEP = 0, CNT_SEL = 1, CNT_LIVE = 2, CNT_ZERO = 4, CNT_SWEEP2 = 5 };   // {0, n_sweep} at 4, 5
 
 // Scalars written by head_step_scalars_kernel.
 enum : int {
@@ -148,6 +149,8 @@ __global__ void __launch_bounds__(1024) head_step_prep_kernel(const StepPrepPara
     q.counts[CNT_SEL] = n_sel;
     q.counts[CNT_LIVE] = n_first;
     q.counts[3] = 0;
+    q.counts[CNT_ZERO] = 0;       // the row range [0, n_sweep) of the logits-storing sweep
+    q.counts[CNT_SWEEP2] = n_sweep;
     *q.overflow = 0;
     *q.status = 0;
   }
@@ -214,7 +217,70 @@ struct StepRowsParams {
   long long* amax;
   float* top;                             // null, or [m]: the largest logit of every selected row
   float* dx;                              // [m, h] or null (no gradient wanted)
+  // Two-sweep training path (stored logits, head_dx.cuh): the swept rows' statistics come from
+  // the storing forward sweep's partial records (target entry left out of the sums) and their
+  // raw dHidden from the pieces of head_dx_kernel.
+  int stored;                             // 0: single pass; 1: two sweeps
+  int dx_pairs;                           // CTA pairs of the head_dx_kernel launch
+  const float* g_rscale;                  // [m] what the summed pieces of a row are multiplied by
+  const float *g_pm, *g_ps, *g_pt, *g_ptz;
+  const int* g_pidx;
+  const float* pieces;
 };
+
+// Merge of a row's partial records over the vocabulary runs of a forward sweep (kernels.py:70-81):
+// block of 128 threads, thread k reads run k. Returns the maximum, and through the references the
+// sums relative to it, the target logit and the lowest index of the maximum.
+__device__ __forceinline__ float merge_partial_records(const float* pm, const float* ps,
+                                                       const float* pt, const float* ptz,
+                                                       const int* pidx, size_t o0,
+                                                       const FwdSplit& fs, float (*sh_f)[4],
+                                                       int* sh_i, float& s, float& t, float& tz,
+                                                       int& idx) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float mk = NEG_BIG, sk = 0.f, tk = 0.f, tzk = 0.f;
+  int ik = 0x7fffffff;
+  if (static_cast<int>(threadIdx.x) < fs.n_splits) {   // n_splits <= 128 = blockDim
+    const size_t o = o0 + static_cast<size_t>(threadIdx.x) * fs.stride;
+    mk = pm[o];
+    sk = ps[o];
+    tk = pt[o];
+    tzk = ptz[o];
+    ik = pidx[o];
+  }
+  float big = mk;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) big = fmaxf(big, __shfl_xor_sync(0xffffffffu, big, o));
+  if (lane == 0) sh_f[0][warp] = big;
+  __syncthreads();
+  big = fmaxf(fmaxf(sh_f[0][0], sh_f[0][1]), fmaxf(sh_f[0][2], sh_f[0][3]));
+  __syncthreads();
+  const float dl = mk - big;
+  const float sc = __expf(dl);
+  s = sk * sc;
+  t = sc * (tk + sk * dl);
+  tz = tzk;
+  idx = (mk == big) ? ik : 0x7fffffff;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    s += __shfl_xor_sync(0xffffffffu, s, o);
+    t += __shfl_xor_sync(0xffffffffu, t, o);
+    tz += __shfl_xor_sync(0xffffffffu, tz, o);
+    idx = min(idx, __shfl_xor_sync(0xffffffffu, idx, o));
+  }
+  if (lane == 0) {
+    sh_f[0][warp] = s;
+    sh_f[1][warp] = t;
+    sh_f[2][warp] = tz;
+    sh_i[warp] = idx;
+  }
+  __syncthreads();
+  s = sh_f[0][0] + sh_f[0][1] + sh_f[0][2] + sh_f[0][3];
+  t = sh_f[1][0] + sh_f[1][1] + sh_f[1][2] + sh_f[1][3];
+  tz = sh_f[2][0] + sh_f[2][1] + sh_f[2][2] + sh_f[2][3];
+  idx = min(min(sh_i[0], sh_i[1]), min(sh_i[2], sh_i[3]));
+  return big;
+}
 
 template <int kFmt>
 __global__ void __launch_bounds__(128) head_step_rows_kernel(const StepRowsParams q) {
@@ -240,6 +306,57 @@ __global__ void __launch_bounds__(128) head_step_rows_kernel(const StepRowsParam
     o_am = q.f_amax[pos];
     o_top = q.f_max[pos];
     dx_mode = DX_COPY;
+  } else if (pos >= 0 && pos < n_sweep && q.stored != 0) {
+    // ---- two-sweep path: records of the storing forward sweep + pieces of head_dx_kernel ------
+    const FwdSplit fs = fwd_split_rows(n_sweep, q.n_vtiles, q.fwd_pairs, q.part_cap);
+    float s_rest, t, tz;
+    int idx;
+    const float big = merge_partial_records(q.g_pm, q.g_ps, q.g_pt, q.g_ptz, q.g_pidx,
+                                            static_cast<size_t>(pos), fs, sh_f, sh_i, s_rest, t,
+                                            tz, idx);
+    tg = q.tgt_c[pos];
+    const bool valid = tg >= 0;
+    float s = s_rest, p_t = 0.f;
+    if (valid) {   // the target's own term, left out of the sums by the sweep
+      p_t = __expf(tz - big);
+      s += p_t;
+      t += p_t * (tz - big);
+    }
+    const float log_s = logf(s);
+    o_lse = big + log_s;
+    o_ent = log_s - t / s;
+    o_am = idx;
+    o_top = big;
+    o_tl = valid ? tz : 0.f;
+    o_ce = valid ? (s_rest < p_t ? log1pf(s_rest / p_t) : (o_lse - tz)) : 0.f;
+    o_cw = q.cew_c[pos];
+    // dHidden = cew (sum_{v != t} p_v W_v - (1 - p_t) W_t), 1 - p_t = s_rest / s; the pieces hold
+    // the first sum up to the row's factor g_rscale (p is already divided by s)
+    coef = s_rest / s;
+    dx_mode = o_cw != 0.f ? DX_FINISH : DX_ZERO;
+    if (drow != nullptr && dx_mode == DX_FINISH) {
+      const DxSplit ds = dx_split(n_sweep, q.h, q.v, q.dx_pairs);
+      const int rp = pos / dxk::ROWS, rr = pos % dxk::ROWS;
+      const size_t piece = static_cast<size_t>(dxk::ROWS) * dxk::SLICE;
+      const float rs = q.g_rscale[pos];
+      for (int c = threadIdx.x * 4; c < q.h; c += 128 * 4) {
+        const int u = rp * ds.slices + c / dxk::SLICE;
+        const float* src = q.pieces + static_cast<size_t>(u) * piece +
+                           static_cast<size_t>(rr) * dxk::SLICE + (c % dxk::SLICE);
+        float4 rawv = *reinterpret_cast<const float4*>(src);
+        for (int k = 1; k < ds.segs; ++k) {
+          const float4 b = *reinterpret_cast<const float4*>(src + static_cast<size_t>(k) * ds.units * piece);
+          rawv.x += b.x;
+          rawv.y += b.y;
+          rawv.z += b.z;
+          rawv.w += b.w;
+        }
+        const float4 wt = load4_16<kFmt>(q.w, (static_cast<size_t>(tg) * q.h + c) / 4);
+        *reinterpret_cast<float4*>(drow + c) = make_float4(
+            o_cw * (rawv.x * rs - coef * wt.x), o_cw * (rawv.y * rs - coef * wt.y),
+            o_cw * (rawv.z * rs - coef * wt.z), o_cw * (rawv.w * rs - coef * wt.w));
+      }
+    }
   } else if (pos >= 0 && pos < n_sweep) {
     // ---- sweep row: partial statistics, all relative to m_ref ---------------------------------
     const int n_row_tiles = (n_sweep + 127) / 128;

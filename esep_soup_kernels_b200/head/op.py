@@ -215,6 +215,21 @@ class DeviceBackend:
         return dx
 
 
+TRAINING_PATHS = {"auto": 0, "single_pass": 1, "stored_logits": 2}
+
+
+def set_training_path(path="auto"):
+    """Which kernels a call with gradient uses for the rows that need one (process-wide; see
+    ``esep_head_set_training_path`` in include/esep_head.h): "single_pass" keeps the logits on the
+    SM, "stored_logits" keeps them in the workspace as fp16 for a second sweep, "auto" (default)
+    takes the two sweeps where the single pass would need several passes over the hidden dimension
+    (hidden > 1536). Returns the previous setting's name."""
+    prev = _lib.load().esep_head_set_training_path(TRAINING_PATHS[path])
+    if prev < 0:
+        _lib.check("esep_head_set_training_path", prev)
+    return {v: k for k, v in TRAINING_PATHS.items()}[prev]
+
+
 def last_device_status(device=None):
     """Synchronises and returns the device status word of the most recent call on ``device``
     (0 = every kernel ran to completion; see include/esep_head.h). Raises on a non-zero word."""

@@ -296,11 +296,25 @@ int esep_embed_rows(const void* w16, const int64_t* ids, int64_t n, int64_t v, i
 int esep_weight_exact(const void* w16, int64_t v, int64_t h, int64_t count,
                       const int64_t* flat_idx, const float* flat_val, float* out, void* stream);
 
+/* Which kernels a call with gradient runs over the rows that need one.
+ *   single pass  - head_train_kernel (8-CTA clusters at hidden 3200 - 3584): the logits never
+ *                  leave the SM; smallest workspace;
+ *   two sweeps   - a forward sweep that keeps (logit - reference maximum) log2 e as fp16 in the
+ *                  workspace (rows x vocabulary x 2 bytes), then dHidden from those logits
+ *                  (head_dx_kernel). Needs hidden % 64 == 0 and at most 48 GiB of stored logits.
+ * path 0 (default): two sweeps where the single pass would need more than one pass over the hidden
+ * dimension (hidden > 1536), else the single pass - the faster choice on B200 in both cases;
+ * 1: always the single pass; 2: two sweeps wherever they apply. Process-wide, read when a call
+ * (or a workspace query) is made: set it before sizing the workspace. Returns the previous value,
+ * or ESEP_ERR_BAD_ARG. No counterpart in the reference (its chunk loop is one path). */
+int esep_head_set_training_path(int path);
+
 /* Counters: out[0] = per-device initialisations performed so far (function attributes,
  * occupancy queries), out[1] = tensor maps encoded so far (maps are cached by address and
  * shape) - a warmed-up process that repeats a call sees neither number move; out[2] (n >= 3) =
  * kernels launched by the library so far, over all entry points and threads; out[3] (n >= 4) =
- * how many of those were the 8-CTA-cluster training sweep (hidden sizes of 3200 - 3584). */
+ * how many of those were the 8-CTA-cluster training sweep (hidden sizes of 3200 - 3584);
+ * out[4] (n >= 5) = how many were the dHidden-from-stored-logits kernel. */
 int esep_head_debug_counters(long long* out, int n);
 
 /* ---- the step either side of the head: final residual add + RMSNorm ------------------------- */

@@ -292,6 +292,8 @@ def test_hidden_of_three_passes_runs_as_one_pass_on_eight_cta_clusters(n, h, v, 
         assert _lib.load().esep_head_debug_counters(buf, 4) == 0
         return buf[3]
 
+    from esep_soup_kernels_b200.head.op import set_training_path
+
     g = torch.Generator().manual_seed(n + h + v)
     w = (torch.randn(v, h, generator=g) * (1.0 / h ** 0.5)).to(dtype)
     x = torch.randn(n, h, generator=g).to(dtype)
@@ -300,12 +302,87 @@ def test_hidden_of_three_passes_runs_as_one_pass_on_eight_cta_clusters(n, h, v, 
     c = torch.rand(n, generator=g)
     c[t < 0] = 0.0
     before = wide_launches()
-    loss, stats, dx = run_op(x, w, t, c)
-    assert wide_launches() == before + 1
-    check_against_oracle(x, w, t, c, loss, stats, dx)
-    assert dx[::17].abs().max().item() == 0.0
-    loss2, stats2, dx2 = run_op(x, w, t, c)
-    assert torch.equal(loss, loss2) and torch.equal(dx, dx2)
+    set_training_path("single_pass")      # at these sizes the default is the two-sweep path
+    try:
+        loss, stats, dx = run_op(x, w, t, c)
+        assert wide_launches() == before + 1
+        check_against_oracle(x, w, t, c, loss, stats, dx)
+        assert dx[::17].abs().max().item() == 0.0
+        loss2, stats2, dx2 = run_op(x, w, t, c)
+        assert torch.equal(loss, loss2) and torch.equal(dx, dx2)
+    finally:
+        set_training_path("auto")
+
+
+def _dx_launches():
+    import ctypes
+    from esep_soup_kernels_b200.head import _lib
+
+    buf = (ctypes.c_longlong * 5)()
+    assert _lib.load().esep_head_debug_counters(buf, 5) == 0
+    return buf[4]
+
+
+@pytest.mark.parametrize("n,h,v,dtype,peak", [
+    (300, 128, 5003, torch.float16, 25.0),     # the reference's unit-test shape, peaked targets
+    (513, 1536, 3000, torch.float16, 30.0),    # real hidden size, ragged rows and vocabulary
+    (1, 64, 257, torch.bfloat16, 0.0),         # one row, vocabulary just over one tile
+    (700, 3584, 6000, torch.bfloat16, 10.0),   # 7B hidden: seven 512-column slices
+    (2600, 704, 2100, torch.bfloat16, 5.0),    # eleven row pairs x two slices (the second ragged)
+    (129, 192, 40000, torch.float16, 0.0),     # few units, long vocabulary: cut into runs
+])
+def test_two_sweeps_over_stored_logits_match_the_oracle(n, h, v, dtype, peak):
+    """The training path that keeps the logits: forward sweep storing (logit - reference maximum)
+    log2 e as fp16, then dHidden from the stored logits (P = one packed 2^x per two entries, the
+    target's own term added in fp32). Same outputs, same tolerances, bit-identical when repeated;
+    exact zeros on rows without a loss; the library's counter shows that the kernel ran."""
+    from esep_soup_kernels_b200.head.op import set_training_path
+
+    x, w, t, c = _peaked(n, h, v, 1.0 / h ** 0.5, peak, n + h, dtype=dtype)
+    set_training_path("stored_logits")
+    try:
+        before = _dx_launches()
+        loss, stats, dx = run_op(x, w, t, c)
+        assert _dx_launches() == before + 1
+        check_against_oracle(x, w, t, c, loss, stats, dx)
+        assert dx[::7].abs().max().item() == 0.0
+        loss2, stats2, dx2 = run_op(x, w, t, c)
+        assert torch.equal(loss, loss2) and torch.equal(dx, dx2)
+        for k in stats:
+            assert torch.equal(stats[k], stats2[k])
+        # many rows without a loss: they take the statistics-only sweep, the others this path
+        t[: n // 2] = -100
+        c[: n // 2] = 0.0
+        loss3, stats3, dx3 = run_op(x, w, t, c)
+        check_against_oracle(x, w, t, c, loss3, stats3, dx3)
+        assert n < 2 or dx3[: n // 2].abs().max().item() == 0.0
+    finally:
+        set_training_path("auto")
+
+
+def test_default_path_by_hidden_size_and_agreement_of_the_two_paths():
+    """Default: the single pass up to hidden 1536, the two sweeps above it. Both paths agree to
+    the rounding of their 16-bit softmax weights."""
+    from esep_soup_kernels_b200.head.op import set_training_path
+
+    x, w, t, c = _peaked(400, 1536, 5000, 0.03, 8.0, 21, dtype=torch.bfloat16)
+    before = _dx_launches()
+    run_op(x, w, t, c)
+    assert _dx_launches() == before                    # single pass
+    x2, w2, t2, c2 = _peaked(400, 2048, 5000, 0.03, 8.0, 22, dtype=torch.bfloat16)
+    loss_a, stats_a, dx_a = run_op(x2, w2, t2, c2)
+    assert _dx_launches() == before + 1                # two sweeps
+    assert set_training_path("single_pass") == "auto"
+    try:
+        loss_b, stats_b, dx_b = run_op(x2, w2, t2, c2)
+        assert _dx_launches() == before + 1
+    finally:
+        assert set_training_path("auto") == "single_pass"
+    torch.testing.assert_close(loss_a, loss_b, rtol=1e-5, atol=1e-7)
+    torch.testing.assert_close(stats_a["lse"], stats_b["lse"], rtol=1e-5, atol=2e-5)
+    assert torch.equal(stats_a["argmax"], stats_b["argmax"])
+    rel = ((dx_a.float() - dx_b.float()).norm() / dx_b.float().norm()).item()
+    assert rel < 5e-3, rel
 
 
 def test_rows_without_a_loss_term_take_the_forward_sweep_and_get_zero_gradient():
@@ -603,10 +680,20 @@ def test_single_sweep_falls_back_when_a_row_maximum_is_far_above_the_prefix():
         loss, stats, dx = run_op(x, w, t, c)
         assert not last_call_fell_back("cuda:0")
         check_against_oracle(x, w, t, c, loss, stats, dx)
-    # the same guard behind the 8-CTA-cluster sweep (hidden 3584)
+    # the same guard behind the 8-CTA-cluster sweep (hidden 3584, single pass asked for); the
+    # two-sweep path these sizes take by default knows the true maximum and needs no guard
+    from esep_soup_kernels_b200.head.op import set_training_path
+
     x, w, t, c = _planted_outlier_case(600.0, h=3584)
+    set_training_path("single_pass")
+    try:
+        loss, stats, dx = run_op(x, w, t, c)
+        assert last_call_fell_back("cuda:0")
+        check_against_oracle(x, w, t, c, loss, stats, dx)
+    finally:
+        set_training_path("auto")
     loss, stats, dx = run_op(x, w, t, c)
-    assert last_call_fell_back("cuda:0")
+    assert not last_call_fell_back("cuda:0")
     check_against_oracle(x, w, t, c, loss, stats, dx)
 
 
