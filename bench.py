@@ -580,8 +580,8 @@ def _vocab_parallel_c4(dist, par, make_config, make_weight, shape, dev, rank, wo
            "dtype": "bfloat16", "steps": steps, "ms_per_step": ms, "tokens_s": n / (ms * 1e-3),
            "tensor_frac": f_alg_gpu / (ms * 1e-3) / 1e12 / peaks["tflops"],
            "time_split_rank0": split, "dx_identical_on_all_ranks": bool((lo_chk == hi_chk).all()),
-           "note": "hidden 3584 runs on 8-CTA clusters that hold all 28 accumulator blocks (4 CTAs "
-                   "compute logits and P, all 8 accumulate dHidden): one pass, logits computed once"}
+           "note": "hidden 3584 takes the two-sweep path: a forward sweep keeps the logits as fp16 in "
+                   "HBM, head_dx_kernel turns them into dHidden (CTA pairs, 256 rows per W tile)"}
     # parity: the oracle needs the whole W on the host; rank 0 rebuilds the other shards
     sub = torch.arange(0, n, n // 64)[:64]
     if rank == 0:
