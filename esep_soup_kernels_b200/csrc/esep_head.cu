@@ -946,8 +946,14 @@ int step_layout(int64_t m, int64_t h, int64_t v, bool need_grad, const DeviceInf
       t->stored = true;
   }
   const size_t mr = static_cast<size_t>(div_up(m, 256)) * 256;
-  t->part_cap = static_cast<int>(std::min<size_t>(mr + static_cast<size_t>(4) * 256 * d->max_pairs_fwd,
-                                                  static_cast<size_t>(1) << 30));
+  // Rows of the forward partial arrays: room for 16 vocabulary runs per row (the split search of
+  // fwd_split_rows then reaches 97 % of the pairs for any row count: with 3 runs, 128 row pairs on
+  // 74 CTA pairs lose 13 % to the last wave), bounded for very large batches.
+  {
+    const size_t few = mr + static_cast<size_t>(4) * 256 * d->max_pairs_fwd;
+    const size_t many = std::min<size_t>(16 * mr, static_cast<size_t>(1) << 22);
+    t->part_cap = static_cast<int>(std::min<size_t>(std::max(few, many), static_cast<size_t>(1) << 30));
+  }
   const size_t f4 = sizeof(float);
   size_t off = align_up(std::max(pl.ws_bytes, pre.ws_bytes));
   t->base_bytes = off;
