@@ -350,12 +350,12 @@ head_dx_kernel(const __grid_constant__ CUtensorMap tmap_w,   // W as {64 h, v, h
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             // two entries per instruction: P = 2^(d + k) <= 2^10.5 in fp16
-            const __half2 pe =
-                h2exp2(__hadd2(*reinterpret_cast<const __half2*>(&in[e]), k2r[it & 1]));
+            const __half2 arg = __hadd2(*reinterpret_cast<const __half2*>(&in[e]), k2r[it & 1]);
+            const uint32_t pe = ex2_approx_f16x2(*reinterpret_cast<const uint32_t*>(&arg));
             if (kFmt == 0) {
-              out[e] = *reinterpret_cast<const uint32_t*>(&pe);
+              out[e] = pe;
             } else {
-              const float2 pf = __half22float2(pe);
+              const float2 pf = __half22float2(*reinterpret_cast<const __half2*>(&pe));
               out[e] = pack2<1>(pf.x, pf.y);
             }
           }

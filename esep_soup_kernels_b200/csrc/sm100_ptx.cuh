@@ -342,6 +342,14 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap
       : "memory");
 }
 
+// 2^x of two fp16 values in ONE instruction (cuda_fp16's h2exp2 goes through fp32: two
+// conversions each way, two fp32 ex2 and two corrections per pair).
+__device__ __forceinline__ uint32_t ex2_approx_f16x2(uint32_t x) {
+  uint32_t y;
+  asm("ex2.approx.f16x2 %0, %1;" : "=r"(y) : "r"(x));
+  return y;
+}
+
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
