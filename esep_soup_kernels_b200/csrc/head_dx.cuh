@@ -355,8 +355,15 @@ head_dx_kernel(const __grid_constant__ CUtensorMap tmap_w,   // W as {64 h, v, h
             if (kFmt == 0) {
               out[e] = pe;
             } else {
-              const float2 pf = __half22float2(*reinterpret_cast<const __half2*>(&pe));
-              out[e] = pack2<1>(pf.x, pf.y);
+              // fp16 -> bf16 of two positive values with integer operations (the conversion
+              // instructions share the XU pipe with the 2^x and would triple its load): round the
+              // 10-bit mantissa to 7 bits (to nearest, ties to even), move the exponent (bias 15 -> 127), and keep zero for
+              // what fp16 holds as zero or subnormal (below 2^-14 of a scale of 2^10).
+              const uint32_t rne = pe + 0x00030003u + ((pe >> 3) & 0x00010001u);   // ties to even
+              const uint32_t r = ((rne >> 3) & 0x1FFF1FFFu) + 0x38003800u;
+              const uint32_t keep = ((pe & 0x0000FC00u) ? 0x0000FFFFu : 0u) |
+                                    ((pe & 0xFC000000u) ? 0xFFFF0000u : 0u);
+              out[e] = r & keep;
             }
           }
           // the target's entry (once per row and run): 0..7 when it sits in this group
