@@ -894,6 +894,7 @@ struct StepLayout {
   int rows_nhb;        // accumulator blocks per quarter of a pass, as the row-finish kernel sees it
   int pass_w;          // columns per pass = row stride of the partial dHidden pieces
   bool stored;         // two sweeps: forward sweep that stores the logits, then head_dx_kernel
+  bool both;           // both paths are enqueued and the device picks one from the row count
   size_t zpitch;       // elements per row of the stored logits
   size_t z_off, c2_off, partg_off, pieces_off;
   int part_cap;        // rows of the forward partial arrays
@@ -933,6 +934,7 @@ int step_layout(int64_t m, int64_t h, int64_t v, bool need_grad, const DeviceInf
         std::min<int64_t>(d->max_clusters_wide, n_tp * pl.bwd_total_steps));
   }
   t->stored = false;
+  t->both = false;
   t->zpitch = static_cast<size_t>(pl.fwd_vocab_tiles) * 256;
   {
     const int path = g_training_path.load();
@@ -941,9 +943,12 @@ int step_layout(int64_t m, int64_t h, int64_t v, bool need_grad, const DeviceInf
     // single pass is the faster one (3.55 against 3.72 ms at 4 340 x 1536 x 151 936); above it the
     // two sweeps are (hidden 3584, 32 768 x 19 008: 10.1 against 13.5 ms on 8-CTA clusters).
     const bool wanted = path == 2 || (path == 0 && pl.bwd_passes > 1);
-    if (need_grad && wanted && d->max_pairs_dx > 0 && h % 64 == 0 &&
-        zbytes <= kMaxStoredLogitsBytes)
-      t->stored = true;
+    const bool possible = need_grad && d->max_pairs_dx > 0 && h % 64 == 0 &&
+                          zbytes <= kMaxStoredLogitsBytes;
+    if (possible && wanted) t->stored = true;
+    // one pass over the hidden dimension: the single pass is the faster one unless the row count
+    // leaves many of its clusters idle, which only the device knows (head_step_prep_kernel)
+    t->both = possible && path == 0 && !t->stored;
   }
   const size_t mr = static_cast<size_t>(div_up(m, 256)) * 256;
   // Rows of the forward partial arrays: room for 16 vocabulary runs per row (the split search of
@@ -975,7 +980,7 @@ int step_layout(int64_t m, int64_t h, int64_t v, bool need_grad, const DeviceInf
   t->st_off = t->lo_off = t->dxpart_off = t->dxc_off = t->fb_off = t->fbam_off = t->floss_off = off;
   t->st_stride = t->lo_stride = t->fb_stride = 0;
   if (need_grad) t->record_off = take(static_cast<size_t>(ESEP_RECORD_FIELDS) * m * f4);
-  if (need_grad && !t->stored) {
+  if (need_grad && (!t->stored || t->both)) {
     t->st_stride = align_up(static_cast<size_t>(16) * m * f4);
     t->st_off = take(4 * t->st_stride);
     // a left-over pair is cut into at most ncl / rem_tp runs: rem_tp * rem_splits <= ncl
@@ -989,7 +994,7 @@ int step_layout(int64_t m, int64_t h, int64_t v, bool need_grad, const DeviceInf
     t->floss_off = take(kAlign);
   }
   t->z_off = t->c2_off = t->partg_off = t->pieces_off = off;
-  if (t->stored) {
+  if (t->stored || t->both) {
     t->z_off = take(static_cast<size_t>(m) * t->zpitch * 2);
     t->c2_off = take(2 * align_up(static_cast<size_t>(m) * f4));   // kexp, rscale
     t->partg_off = take(5 * t->part_stride);
@@ -1105,6 +1110,9 @@ int step_impl(const StepArgs& a) {
   q.counts = counts;
   q.overflow = overflow;
   q.status = status;
+  q.path_mode = t.both ? 2 : (t.stored ? 1 : 0);
+  q.sweep_clusters = t.ncl;
+  q.sweep_steps = pl.bwd_total_steps;
   head_step_prep_kernel<<<1, 1024, 0, s>>>(q);
   if (cudaGetLastError() != cudaSuccess) return ESEP_ERR_CUDA;
   g_launches.fetch_add(1);
@@ -1139,7 +1147,7 @@ int step_impl(const StepArgs& a) {
   const unsigned fwd_grid = static_cast<unsigned>(2 * d->max_pairs_fwd);
   float* part_g = reinterpret_cast<float*>(ws + t.partg_off);
   const size_t psg = t.part_stride / sizeof(float);
-  if (need_grad && t.stored) {
+  if (need_grad && (t.stored || t.both)) {
     // 4a. forward sweep over the compact rows [0, n_sweep) that keeps logit - m_ref as fp16
     CUtensorMap tx, tw;
     if (make_tmap(&tx, xc, a.dtype, a.m, a.h, fwd::BK, fwd::BM) != ESEP_OK) return ESEP_ERR_CUDA;
@@ -1178,7 +1186,7 @@ int step_impl(const StepArgs& a) {
     float* kexp = reinterpret_cast<float*>(ws + t.c2_off);
     float* rscale = reinterpret_cast<float*>(ws + t.c2_off + align_up(static_cast<size_t>(m) * sizeof(float)));
     const unsigned rc_grid = static_cast<unsigned>(div_up(m, 128));
-    head_dx_rowconst_kernel<<<rc_grid, 128, 0, s>>>(m, counts + CNT_SWEEP, pl.fwd_vocab_tiles,
+    head_dx_rowconst_kernel<<<rc_grid, 128, 0, s>>>(m, counts + CNT_STORE, pl.fwd_vocab_tiles,
                                                     static_cast<int>(fwd_grid / 2), t.part_cap, g.pm,
                                                     g.ps, g.ptz, tgt_c, v, record, kexp, rscale);
     if (cudaGetLastError() != cudaSuccess) return ESEP_ERR_CUDA;
@@ -1189,7 +1197,7 @@ int step_impl(const StepArgs& a) {
     dp.n = m;
     dp.h = h;
     dp.v = v;
-    dp.n_dev = counts + CNT_SWEEP;
+    dp.n_dev = counts + CNT_STORE;
     dp.z = g.zbuf;
     dp.zpitch = g.zpitch;
     dp.kexp = kexp;
@@ -1205,7 +1213,7 @@ int step_impl(const StepArgs& a) {
     if (st != ESEP_OK) return st;
     g_dx_launches.fetch_add(1);
   }
-  if (need_grad && !t.stored) {
+  if (need_grad && (!t.stored || t.both)) {
     // 4. the training sweep over the compact rows [0, n_sweep)
     CUtensorMap tx, tw1, tw2, tw2b;
     if (make_tmap(&tx, xc, a.dtype, a.m, a.h, bwd::BK, 64) != ESEP_OK) return ESEP_ERR_CUDA;
@@ -1220,7 +1228,7 @@ int step_impl(const StepArgs& a) {
     p.n = m;
     p.h = h;
     p.v = v;
-    p.n_dev = counts + CNT_SWEEP;
+    p.n_dev = counts + CNT_TRAIN;
     p.nhb = pl.bwd_hblocks;
     p.total_steps = pl.bwd_total_steps;
     p.m_ref = record;
@@ -1318,7 +1326,7 @@ int step_impl(const StepArgs& a) {
   float* fb = reinterpret_cast<float*>(ws + t.fb_off);
   const size_t fbs = t.fb_stride / sizeof(float);
   long long* fb_amax = reinterpret_cast<long long*>(ws + t.fbam_off);
-  if (need_grad && !t.stored) {
+  if (need_grad && (!t.stored || t.both)) {
     // 6. guarded second attempt on the compact rows: the two-kernel path, enqueued behind the
     //    overflow flag. Its kernels return at once unless a row overflowed in the sweep; if one
     //    did, they leave per-row results and final dHidden rows in compact order.
@@ -1367,7 +1375,7 @@ int step_impl(const StepArgs& a) {
   r.amax = reinterpret_cast<long long*>(a.argmax);
   r.top = a.top_logit;
   r.dx = need_grad ? a.dx : nullptr;
-  r.stored = (need_grad && t.stored) ? 1 : 0;
+  r.stored = !need_grad ? 0 : (t.both ? 2 : (t.stored ? 1 : 0));
   r.dx_pairs = d->max_pairs_dx;
   r.g_rscale = reinterpret_cast<const float*>(ws + t.c2_off + align_up(static_cast<size_t>(a.m) * sizeof(float)));
   r.g_pm = part_g;
@@ -1655,6 +1663,21 @@ int esep_weight_exact(const void* w16, int64_t v, int64_t h, int64_t count,
     if (cudaGetLastError() != cudaSuccess) return ESEP_ERR_CUDA;
     g_launches.fetch_add(1);
   }
+  return ESEP_OK;
+}
+
+int esep_head_step_path_taken(const void* workspace, void* stream, int* out_stored) {
+  if (workspace == nullptr || out_stored == nullptr) return ESEP_ERR_BAD_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int v = 0;
+  // the step keeps its row counts at byte 64 of the workspace (CNT_*)
+  if (cudaMemcpyAsync(&v, static_cast<const uint8_t*>(workspace) + 64 + CNT_STORED * sizeof(int),
+                      sizeof(int), cudaMemcpyDeviceToHost, s) != cudaSuccess ||
+      cudaStreamSynchronize(s) != cudaSuccess) {
+    cudaGetLastError();
+    return ESEP_ERR_CUDA;
+  }
+  *out_stored = v;
   return ESEP_OK;
 }
 

@@ -34,6 +34,8 @@
 // read by warps with warp % 4 == 1). Every wait is bounded.
 #pragma once
 
+#include <algorithm>
+
 #include "head_bwd.cuh"
 
 namespace esep {
@@ -96,8 +98,9 @@ __host__ __device__ inline DxSplit dx_split(int n_rows, int h, int v, int n_pair
 }
 // Upper bound of dx_split(n', ...).runs over all n' <= n_rows (pieces the buffer must hold).
 __host__ inline long long dx_max_runs(int n_rows, int h, int v, int n_pairs) {
-  const DxSplit full = dx_split(n_rows, h, v, n_pairs);
-  return full.units > 8LL * n_pairs ? full.units : 8LL * n_pairs;
+  const DxSplit full = dx_split(n_rows, h, v, n_pairs);   // units grow with the rows; segs <= 16
+  const long long cut = std::min<long long>(8LL * n_pairs, 16LL * full.units);
+  return std::max<long long>(full.units, cut);
 }
 
 struct DxParams {
@@ -118,6 +121,7 @@ __global__ void __launch_bounds__(dxk::THREADS, 1)
 head_dx_kernel(const __grid_constant__ CUtensorMap tmap_w,   // W as {64 h, v, h/64}, box {64, 32, 4}
                const DxParams p) {
   using namespace dxk;
+  if (min(*p.n_dev, p.n) <= 0) return;   // no rows on this path (every CTA reads the same count)
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;

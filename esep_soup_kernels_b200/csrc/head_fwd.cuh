@@ -196,6 +196,7 @@ head_fwd_kernel(const __grid_constant__ CUtensorMap tmap_x,
                 const __grid_constant__ CUtensorMap tmap_w, const FwdParams p) {
   using namespace fwd;
   if (p.gate != nullptr && *p.gate == 0) return;   // guarded launch: not needed this time
+  if (p.row_range != nullptr && p.row_range[1] <= p.row_range[0]) return;   // no rows to sweep
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;  // 128-byte swizzle wants 1024-byte tiles

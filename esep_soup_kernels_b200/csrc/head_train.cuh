@@ -113,6 +113,7 @@ head_train_kernel(const __grid_constant__ CUtensorMap tmap_x,    // x [n, h], bo
                                                                  // {64, 32, 6} (or 2-D, {64 h, 32 v})
                   const TrainParams p) {
   using namespace trn;
+  if (p.n_dev != nullptr && *p.n_dev <= 0) return;   // no rows on this path (same for every CTA)
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;

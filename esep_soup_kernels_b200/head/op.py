@@ -246,6 +246,20 @@ def last_device_status(device=None):
     return out.value
 
 
+def last_call_used_stored_logits(device=None):
+    """True if the most recent call with gradient on the device took the two-sweep path (the
+    choice is made on the device for hidden sizes up to 1536). Synchronises (a test aid)."""
+    index = torch.cuda.current_device() if device is None else torch.device(device).index
+    with _state_lock:
+        ws = _last_workspace.get(index)
+    if ws is None:
+        return False
+    out = ctypes.c_int(0)
+    _lib.check("esep_head_step_path_taken", _lib.load().esep_head_step_path_taken(
+        _ptr(ws), _stream(ws.device), ctypes.byref(out)))
+    return out.value != 0
+
+
 def last_call_fell_back(device=None):
     """True if the most recent single-pass call on the device raised its overflow flag, i.e. its
     outputs came from the guarded two-kernel path. Synchronises (a test / monitoring aid)."""

@@ -303,11 +303,19 @@ int esep_weight_exact(const void* w16, int64_t v, int64_t h, int64_t count,
  *                  workspace (rows x vocabulary x 2 bytes), then dHidden from those logits
  *                  (head_dx_kernel). Needs hidden % 64 == 0 and at most 48 GiB of stored logits.
  * path 0 (default): two sweeps where the single pass would need more than one pass over the hidden
- * dimension (hidden > 1536), else the single pass - the faster choice on B200 in both cases;
- * 1: always the single pass; 2: two sweeps wherever they apply. Process-wide, read when a call
- * (or a workspace query) is made: set it before sizing the workspace. Returns the previous value,
- * or ESEP_ERR_BAD_ARG. No counterpart in the reference (its chunk loop is one path). */
+ * dimension (hidden > 1536). Up to hidden 1536 BOTH are enqueued and the device takes one from the
+ * number of rows with a gradient (known only there): the single pass - the faster one at these
+ * sizes - unless its whole-tile work split would leave more than 15 % of its clusters idle (e.g.
+ * 17 row tiles on 33 clusters), then the two sweeps, whose split is finer; the kernels of the
+ * path not taken return at once. 1: always the single pass (no logits buffer in the workspace);
+ * 2: two sweeps wherever they apply. Process-wide, read when a call (or a workspace query) is made:
+ * set it before sizing the workspace. Returns the previous value, or ESEP_ERR_BAD_ARG. No
+ * counterpart in the reference (its chunk loop is one path). */
 int esep_head_set_training_path(int path);
+
+/* Which of the two the most recent esep_head_step on this workspace took (*out_stored = 1: two
+ * sweeps). Synchronises the stream (a test / monitoring aid). */
+int esep_head_step_path_taken(const void* workspace, void* stream, int* out_stored);
 
 /* Counters: out[0] = per-device initialisations performed so far (function attributes,
  * occupancy queries), out[1] = tensor maps encoded so far (maps are cached by address and

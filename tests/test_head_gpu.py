@@ -360,22 +360,27 @@ def test_two_sweeps_over_stored_logits_match_the_oracle(n, h, v, dtype, peak):
         set_training_path("auto")
 
 
-def test_default_path_by_hidden_size_and_agreement_of_the_two_paths():
-    """Default: the single pass up to hidden 1536, the two sweeps above it. Both paths agree to
-    the rounding of their 16-bit softmax weights."""
-    from esep_soup_kernels_b200.head.op import set_training_path
+def test_default_path_by_hidden_size_and_row_count_and_agreement_of_the_two_paths():
+    """Default: two sweeps above hidden 1536; up to 1536 the device picks from the number of rows
+    with a gradient - the single pass unless its whole-tile split would idle many clusters (17 to
+    28 row tiles on 33 clusters), then the two sweeps. Both paths agree to the rounding of their
+    16-bit softmax weights."""
+    from esep_soup_kernels_b200.head.op import last_call_used_stored_logits, set_training_path
 
     x, w, t, c = _peaked(400, 1536, 5000, 0.03, 8.0, 21, dtype=torch.bfloat16)
-    before = _dx_launches()
     run_op(x, w, t, c)
-    assert _dx_launches() == before                    # single pass
+    assert not last_call_used_stored_logits("cuda:0")       # 4 row tiles: cut into vocabulary runs
+    x1, w1, t1, c1 = _peaked(2800, 1536, 3000, 0.03, 8.0, 23, dtype=torch.float16)
+    loss1, stats1, dx1 = run_op(x1, w1, t1, c1)             # 2 400 live rows = 19 tiles
+    assert last_call_used_stored_logits("cuda:0")
+    check_against_oracle(x1, w1, t1, c1, loss1, stats1, dx1)
     x2, w2, t2, c2 = _peaked(400, 2048, 5000, 0.03, 8.0, 22, dtype=torch.bfloat16)
     loss_a, stats_a, dx_a = run_op(x2, w2, t2, c2)
-    assert _dx_launches() == before + 1                # two sweeps
+    assert last_call_used_stored_logits("cuda:0")           # hidden > 1536
     assert set_training_path("single_pass") == "auto"
     try:
         loss_b, stats_b, dx_b = run_op(x2, w2, t2, c2)
-        assert _dx_launches() == before + 1
+        assert not last_call_used_stored_logits("cuda:0")
     finally:
         assert set_training_path("auto") == "single_pass"
     torch.testing.assert_close(loss_a, loss_b, rtol=1e-5, atol=1e-7)
