@@ -279,9 +279,7 @@ head_dx_kernel(const __grid_constant__ CUtensorMap tmap_w,   // W as {64 h, v, h
       }
     }
   } else {
-    // ------------------- transform warps: logits -> P in place; drain at the end of a run
-    constexpr int TT = T_WARPS * 32;            // 512 transform threads
-    constexpr int GROUPS = P_SLOT / 16 / TT;    // 16-byte groups per thread and step: 4
+    // ------------------- transform warps: logits -> P; drain at the end of a run ----------
     const int quad = warp & 3;                  // TMEM lane quadrant this warp may read
     const bool does_transform = quad != 1;
     const int tt = ((warp - 2) - ((warp - 1) >> 2)) * 32 + lane;   // 0..511 among the transformers
