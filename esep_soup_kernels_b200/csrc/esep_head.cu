@@ -894,7 +894,6 @@ struct StepLayout {
   int rows_nhb;        // accumulator blocks per quarter of a pass, as the row-finish kernel sees it
   int pass_w;          // columns per pass = row stride of the partial dHidden pieces
   bool stored;         // two sweeps: forward sweep that stores the logits, then head_dx_kernel
-  bool both;           // both paths are enqueued and the device picks one from the row count
   size_t zpitch;       // elements per row of the stored logits
   size_t z_off, c2_off, partg_off, pieces_off;
   int part_cap;        // rows of the forward partial arrays
@@ -934,21 +933,17 @@ int step_layout(int64_t m, int64_t h, int64_t v, bool need_grad, const DeviceInf
         std::min<int64_t>(d->max_clusters_wide, n_tp * pl.bwd_total_steps));
   }
   t->stored = false;
-  t->both = false;
   t->zpitch = static_cast<size_t>(pl.fwd_vocab_tiles) * 256;
   {
     const int path = g_training_path.load();
     const size_t zbytes = static_cast<size_t>(m) * t->zpitch * 2;
-    // Measured on B200: where one 4-CTA cluster holds the whole dHidden accumulator (H <= 1536) the
-    // single pass is the faster one (3.55 against 3.72 ms at 4 340 x 1536 x 151 936); above it the
-    // two sweeps are (hidden 3584, 32 768 x 19 008: 10.1 against 13.5 ms on 8-CTA clusters).
-    const bool wanted = path == 2 || (path == 0 && pl.bwd_passes > 1);
-    const bool possible = need_grad && d->max_pairs_dx > 0 && h % 64 == 0 &&
-                          zbytes <= kMaxStoredLogitsBytes;
-    if (possible && wanted) t->stored = true;
-    // one pass over the hidden dimension: the single pass is the faster one unless the row count
-    // leaves many of its clusters idle, which only the device knows (head_step_prep_kernel)
-    t->both = possible && path == 0 && !t->stored;
+    // Measured on B200 (same box, alternating): two sweeps 3.41 against 3.55 ms at 4 340 x 1536 x
+    // 151 936, 13.7 against 14.4 ms at 16 384 rows, 9.7 against 13.5 ms at the 7B shard shape
+    // (32 768 x 3584 x 19 008, single pass on 8-CTA clusters): they are the default wherever they
+    // apply; the single pass remains for callers that cannot spare the logits buffer (path 1).
+    if (need_grad && path != 1 && d->max_pairs_dx > 0 && h % 64 == 0 &&
+        zbytes <= kMaxStoredLogitsBytes)
+      t->stored = true;
   }
   const size_t mr = static_cast<size_t>(div_up(m, 256)) * 256;
   // Rows of the forward partial arrays: room for 16 vocabulary runs per row (the split search of
@@ -980,7 +975,7 @@ int step_layout(int64_t m, int64_t h, int64_t v, bool need_grad, const DeviceInf
   t->st_off = t->lo_off = t->dxpart_off = t->dxc_off = t->fb_off = t->fbam_off = t->floss_off = off;
   t->st_stride = t->lo_stride = t->fb_stride = 0;
   if (need_grad) t->record_off = take(static_cast<size_t>(ESEP_RECORD_FIELDS) * m * f4);
-  if (need_grad && (!t->stored || t->both)) {
+  if (need_grad && !t->stored) {
     t->st_stride = align_up(static_cast<size_t>(16) * m * f4);
     t->st_off = take(4 * t->st_stride);
     // a left-over pair is cut into at most ncl / rem_tp runs: rem_tp * rem_splits <= ncl
@@ -994,7 +989,7 @@ int step_layout(int64_t m, int64_t h, int64_t v, bool need_grad, const DeviceInf
     t->floss_off = take(kAlign);
   }
   t->z_off = t->c2_off = t->partg_off = t->pieces_off = off;
-  if (t->stored || t->both) {
+  if (t->stored) {
     t->z_off = take(static_cast<size_t>(m) * t->zpitch * 2);
     t->c2_off = take(2 * align_up(static_cast<size_t>(m) * f4));   // kexp, rscale
     t->partg_off = take(5 * t->part_stride);
@@ -1110,9 +1105,7 @@ int step_impl(const StepArgs& a) {
   q.counts = counts;
   q.overflow = overflow;
   q.status = status;
-  q.path_mode = t.both ? 2 : (t.stored ? 1 : 0);
-  q.sweep_clusters = t.ncl;
-  q.sweep_steps = pl.bwd_total_steps;
+  q.stored = t.stored ? 1 : 0;
   head_step_prep_kernel<<<1, 1024, 0, s>>>(q);
   if (cudaGetLastError() != cudaSuccess) return ESEP_ERR_CUDA;
   g_launches.fetch_add(1);
@@ -1147,7 +1140,7 @@ int step_impl(const StepArgs& a) {
   const unsigned fwd_grid = static_cast<unsigned>(2 * d->max_pairs_fwd);
   float* part_g = reinterpret_cast<float*>(ws + t.partg_off);
   const size_t psg = t.part_stride / sizeof(float);
-  if (need_grad && (t.stored || t.both)) {
+  if (need_grad && t.stored) {
     // 4a. forward sweep over the compact rows [0, n_sweep) that keeps logit - m_ref as fp16
     CUtensorMap tx, tw;
     if (make_tmap(&tx, xc, a.dtype, a.m, a.h, fwd::BK, fwd::BM) != ESEP_OK) return ESEP_ERR_CUDA;
@@ -1213,7 +1206,7 @@ int step_impl(const StepArgs& a) {
     if (st != ESEP_OK) return st;
     g_dx_launches.fetch_add(1);
   }
-  if (need_grad && (!t.stored || t.both)) {
+  if (need_grad && !t.stored) {
     // 4. the training sweep over the compact rows [0, n_sweep)
     CUtensorMap tx, tw1, tw2, tw2b;
     if (make_tmap(&tx, xc, a.dtype, a.m, a.h, bwd::BK, 64) != ESEP_OK) return ESEP_ERR_CUDA;
@@ -1326,7 +1319,7 @@ int step_impl(const StepArgs& a) {
   float* fb = reinterpret_cast<float*>(ws + t.fb_off);
   const size_t fbs = t.fb_stride / sizeof(float);
   long long* fb_amax = reinterpret_cast<long long*>(ws + t.fbam_off);
-  if (need_grad && (!t.stored || t.both)) {
+  if (need_grad && !t.stored) {
     // 6. guarded second attempt on the compact rows: the two-kernel path, enqueued behind the
     //    overflow flag. Its kernels return at once unless a row overflowed in the sweep; if one
     //    did, they leave per-row results and final dHidden rows in compact order.
@@ -1375,7 +1368,7 @@ int step_impl(const StepArgs& a) {
   r.amax = reinterpret_cast<long long*>(a.argmax);
   r.top = a.top_logit;
   r.dx = need_grad ? a.dx : nullptr;
-  r.stored = !need_grad ? 0 : (t.both ? 2 : (t.stored ? 1 : 0));
+  r.stored = (need_grad && t.stored) ? 1 : 0;
   r.dx_pairs = d->max_pairs_dx;
   r.g_rscale = reinterpret_cast<const float*>(ws + t.c2_off + align_up(static_cast<size_t>(a.m) * sizeof(float)));
   r.g_pm = part_g;

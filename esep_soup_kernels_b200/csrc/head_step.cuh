@@ -23,7 +23,7 @@ namespace esep {
 // CNT_SWEEP / CNT_SEL: the compact rows [0, n_sweep) need a gradient, [n_sweep, n_sel) statistics
 // only. CNT_TRAIN: rows the single-pass kernels sweep, {CNT_ZERO, CNT_STORE}: the row range
 // {0, rows} of the logits-storing sweep - one of the two is n_sweep, the other 0 (CNT_STORED says
-// which), so the kernels of the path not taken return at once.
+// which path the call takes).
 enum : int { CNT_SWEEP = 0, CNT_SEL = 1, CNT_LIVE = 2, CNT_TRAIN = 3, CNT_ZERO = 4, CNT_STORE = 5,
              CNT_STORED = 6 };
 
@@ -54,12 +54,7 @@ struct StepPrepParams {
   int* counts;
   int* overflow;             // cleared here
   int* status;               // cleared here
-  // Training path for the rows with a gradient: 0 = single pass, 1 = two sweeps over stored
-  // logits, 2 = decided here from the row count: the single pass hands out whole row tiles, so
-  // with fewer left-over tiles than clusters (but more than half as many) up to half of the GPU
-  // idles; the two-sweep path cuts its work into runs and does not care.
-  int path_mode;
-  int sweep_clusters, sweep_steps;   // geometry of the single pass (path_mode 2)
+  int stored;                // training path of the rows with a gradient: 1 = two sweeps
 };
 
 // Target, weight and selection of caller row r (op.py:105-107; patch.py:446-458).
@@ -159,16 +154,7 @@ __global__ void __launch_bounds__(1024) head_step_prep_kernel(const StepPrepPara
     q.counts[CNT_SWEEP] = n_sweep;
     q.counts[CNT_SEL] = n_sel;
     q.counts[CNT_LIVE] = n_first;
-    int stored = q.path_mode == 1 ? 1 : 0;
-    if (q.path_mode == 2 && n_sweep > 0) {
-      // rounds of the vocabulary the single pass needs against the ideal tiles / clusters
-      const int n_tp = (n_sweep + 127) / 128;
-      const SweepSplit sp = sweep_split(n_tp, q.sweep_clusters, q.sweep_steps);
-      const float rounds = static_cast<float>(sp.full_rounds) +
-                           (sp.rem_tp > 0 ? static_cast<float>(sp.steps_per_split) / q.sweep_steps : 0.f);
-      const float eff = static_cast<float>(n_tp) / (rounds * q.sweep_clusters);
-      stored = eff < 0.85f ? 1 : 0;
-    }
+    const int stored = q.stored;
     q.counts[CNT_TRAIN] = stored ? 0 : n_sweep;
     q.counts[CNT_ZERO] = 0;
     q.counts[CNT_STORE] = stored ? n_sweep : 0;
@@ -242,7 +228,7 @@ struct StepRowsParams {
   // Two-sweep training path (stored logits, head_dx.cuh): the swept rows' statistics come from
   // the storing forward sweep's partial records (target entry left out of the sums) and their
   // raw dHidden from the pieces of head_dx_kernel.
-  int stored;                             // 0: single pass; 1: two sweeps; 2: read counts[CNT_STORED]
+  int stored;                             // 0: single pass; 1: two sweeps
   int dx_pairs;                           // CTA pairs of the head_dx_kernel launch
   const float* g_rscale;                  // [m] what the summed pieces of a row are multiplied by
   const float *g_pm, *g_ps, *g_pt, *g_ptz;
@@ -328,8 +314,7 @@ __global__ void __launch_bounds__(128) head_step_rows_kernel(const StepRowsParam
     o_am = q.f_amax[pos];
     o_top = q.f_max[pos];
     dx_mode = DX_COPY;
-  } else if (pos >= 0 && pos < n_sweep &&
-             (q.stored == 2 ? q.counts[CNT_STORED] != 0 : q.stored != 0)) {
+  } else if (pos >= 0 && pos < n_sweep && q.stored != 0) {
     // ---- two-sweep path: records of the storing forward sweep + pieces of head_dx_kernel ------
     const FwdSplit fs = fwd_split_rows(n_sweep, q.n_vtiles, q.fwd_pairs, q.part_cap);
     float s_rest, t, tz;

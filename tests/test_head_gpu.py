@@ -13,6 +13,17 @@ from tests.helpers import check_against_oracle, run_op
 
 pytestmark = pytest.mark.gpu
 
+
+@pytest.fixture(autouse=True, params=["two_sweeps", "single_pass"])
+def training_path(request):
+    """Every test runs on both training paths of the library: the default (two sweeps over stored
+    logits wherever they apply) and the single pass that keeps the logits on the SM."""
+    from esep_soup_kernels_b200.head.op import set_training_path
+
+    set_training_path("auto" if request.param == "two_sweeps" else "single_pass")
+    yield request.param
+    set_training_path("auto")
+
 GOLDEN = sorted(p for p in glob.glob(os.path.join(os.path.dirname(__file__), "golden", "*.npz"))
                 if not os.path.basename(p).startswith(("final_norm", "fp16_fixup")))   # head cases only
 
@@ -360,26 +371,22 @@ def test_two_sweeps_over_stored_logits_match_the_oracle(n, h, v, dtype, peak):
         set_training_path("auto")
 
 
-def test_default_path_by_hidden_size_and_row_count_and_agreement_of_the_two_paths():
-    """Default: two sweeps above hidden 1536; up to 1536 the device picks from the number of rows
-    with a gradient - the single pass unless its whole-tile split would idle many clusters (17 to
-    28 row tiles on 33 clusters), then the two sweeps. Both paths agree to the rounding of their
-    16-bit softmax weights."""
+def test_default_path_is_the_two_sweeps_and_both_paths_agree():
+    """Default: two sweeps over stored logits wherever they apply (hidden a multiple of 64), the
+    single pass otherwise or when asked for. Both paths agree to the rounding of their 16-bit
+    softmax weights."""
     from esep_soup_kernels_b200.head.op import last_call_used_stored_logits, set_training_path
 
+    set_training_path("auto")
     x, w, t, c = _peaked(400, 1536, 5000, 0.03, 8.0, 21, dtype=torch.bfloat16)
-    run_op(x, w, t, c)
-    assert not last_call_used_stored_logits("cuda:0")       # 4 row tiles: cut into vocabulary runs
-    x1, w1, t1, c1 = _peaked(2800, 1536, 3000, 0.03, 8.0, 23, dtype=torch.float16)
-    loss1, stats1, dx1 = run_op(x1, w1, t1, c1)             # 2 400 live rows = 19 tiles
+    loss_a, stats_a, dx_a = run_op(x, w, t, c)
     assert last_call_used_stored_logits("cuda:0")
-    check_against_oracle(x1, w1, t1, c1, loss1, stats1, dx1)
-    x2, w2, t2, c2 = _peaked(400, 2048, 5000, 0.03, 8.0, 22, dtype=torch.bfloat16)
-    loss_a, stats_a, dx_a = run_op(x2, w2, t2, c2)
-    assert last_call_used_stored_logits("cuda:0")           # hidden > 1536
+    x1, w1, t1, c1 = _peaked(200, 72, 3000, 0.1, 8.0, 23, dtype=torch.float16)
+    run_op(x1, w1, t1, c1)
+    assert not last_call_used_stored_logits("cuda:0")        # hidden 72 is not a multiple of 64
     assert set_training_path("single_pass") == "auto"
     try:
-        loss_b, stats_b, dx_b = run_op(x2, w2, t2, c2)
+        loss_b, stats_b, dx_b = run_op(x, w, t, c)
         assert not last_call_used_stored_logits("cuda:0")
     finally:
         assert set_training_path("auto") == "single_pass"
@@ -670,8 +677,9 @@ def test_single_sweep_falls_back_when_a_row_maximum_is_far_above_the_prefix():
     vocabulary rows (plus a margin of 40). A row whose true maximum is more than 115 above the
     prefix maximum must raise the flag, and the guarded two-kernel path queued in the same call
     must deliver the correct outputs; smaller outliers are handled by the sweep itself."""
-    from esep_soup_kernels_b200.head.op import last_call_fell_back
+    from esep_soup_kernels_b200.head.op import last_call_fell_back, set_training_path
 
+    set_training_path("single_pass")
     x, w, t, c = _planted_outlier_case(600.0)
     z7 = x[7].float() @ w.float().T
     assert float(z7.max() - z7[:2048].max()) > 200.0          # the case is what it claims to be
@@ -685,10 +693,8 @@ def test_single_sweep_falls_back_when_a_row_maximum_is_far_above_the_prefix():
         loss, stats, dx = run_op(x, w, t, c)
         assert not last_call_fell_back("cuda:0")
         check_against_oracle(x, w, t, c, loss, stats, dx)
-    # the same guard behind the 8-CTA-cluster sweep (hidden 3584, single pass asked for); the
-    # two-sweep path these sizes take by default knows the true maximum and needs no guard
-    from esep_soup_kernels_b200.head.op import set_training_path
-
+    # the same guard behind the 8-CTA-cluster sweep (hidden 3584); the two-sweep path knows the
+    # true maximum before it forms a weight and needs no guard
     x, w, t, c = _planted_outlier_case(600.0, h=3584)
     set_training_path("single_pass")
     try:
