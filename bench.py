@@ -49,6 +49,11 @@ def _peaks():
     return {"tflops": 1590.0, "tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
 
 
+def _traffic_sum(*kernels):
+    parts = [_traffic(k) for k in kernels]
+    return None if any(p is None for p in parts) else sum(parts)
+
+
 def _traffic(kernel):
     """DRAM bytes per launch of `kernel` from the committed ncu summary, if one was recorded."""
     path = os.path.join(ROOT, "profiles", "dram_traffic.json")
@@ -426,6 +431,19 @@ def run_ours(args):
                                 "traffic": _traffic("head_bwd_kernel")},
             "note": "the forward sweep also serves rows without a gradient; the pair is the guarded "
                     "second attempt of the single pass and the SINGLE_SWEEP = False path"}
+
+        # ---- the same step on the other training path (logits never leave the SM) ------------
+        head_op.set_training_path("single_pass")
+        try:
+            ms_single = timed(step_device, 10, 3)
+        finally:
+            head_op.set_training_path("auto")
+        single_tf = f_alg / (ms_single * 1e-3) / 1e12
+        line_extra["single_pass_path"] = {
+            "ms_per_step": ms_single, "achieved_tflops": single_tf,
+            "frac": single_tf / peaks["tflops"], "traffic": _traffic("head_train_kernel"),
+            "note": "esep_head_set_training_path(1): head_train_kernel instead of the two sweeps; "
+                    "no logits buffer in the workspace"}
     else:
         line_extra["strong_c3"] = _strong_c3(dist, par, make_config, dev, rank, world, peaks, args)
         line_extra["vocab_parallel_c4"] = _vocab_parallel_c4(dist, par, make_config, make_weight,
@@ -460,18 +478,24 @@ def run_ours(args):
                              "adds the gradient scaling of the autograd backward and, with N > 1, "
                              "NCCL's all-reduce",
         "clocks": clocks,
-        "roofline": {"bound": "tensor", "kernel": "head_train_kernel", "achieved": call_tf,
+        "roofline": {"bound": "tensor",
+                     "kernel": "head_fwd_kernel<store> + head_dx_kernel (the two sweeps of the step: "
+                               "logits GEMM, dHidden GEMM)",
+                     "achieved": call_tf,
                      "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": call_tf / peaks["tflops"],
-                     "traffic": _traffic("head_train_kernel"),
+                     "traffic": _traffic_sum("head_fwd_kernel_store", "head_dx_kernel"),
+                     "traffic_note": "DRAM bytes of the two kernels per step (ncu): the logits are "
+                                     "written once as fp16 (1.27 GB) and read by the second sweep, "
+                                     "W is read by both",
                      "peak_source": peaks["source"] + " burst",
                      "flops": "algorithmic 2*H*V*N + 2*H*V*N_live (logits GEMM + dHidden GEMM, each "
-                              "once); the single pass executes 4*H*V*N",
+                              "once), which is also what the two sweeps execute",
                      "ms": ms_call, "ms_min": min(call_ms), "ms_max": max(call_ms),
                      "ms_first_last": [call_ms[0], call_ms[-1]],
                      "ms_note": "mean over the timed steps of the CUDA-event time of the whole "
                                 "esep_head_step call inside the timed loop (row classes, gather, "
-                                "prefix sweep, training sweep, row finish, scalars, guarded launches); "
-                                "the training sweep is 93 % of it in the ncu launch list"},
+                                "prefix sweep, storing forward sweep, dHidden sweep, row finish, "
+                                "scalars); the two sweeps are 92 % of it in the ncu launch list"},
         "step_tensor_frac": f_alg / (ms_step * 1e-3) / 1e12 / peaks["tflops"],
         "device_status": status,
         "plan": {"sm_count": caps.sm_count, "bwd_clusters_resident": caps.max_clusters_bwd,
