@@ -1057,7 +1057,7 @@ int step_impl(const StepArgs& a) {
     return ESEP_ERR_BAD_ARG;
   const bool need_grad = a.need_grad != 0;
   if (need_grad) {
-    if (a.dx == nullptr || a.w_bf16 == nullptr) return ESEP_ERR_BAD_ARG;
+    if (a.dx == nullptr) return ESEP_ERR_BAD_ARG;
     if ((reinterpret_cast<uintptr_t>(a.dx) & 15u) || (reinterpret_cast<uintptr_t>(a.w_bf16) & 15u))
       return ESEP_ERR_ALIGNMENT;
   }
@@ -1067,6 +1067,8 @@ int step_impl(const StepArgs& a) {
   StepLayout t;
   st = step_layout(a.m, a.h, a.v, need_grad, d, &t);
   if (st != ESEP_OK) return st;
+  // the bf16 copy of W is read by the single pass only (the two sweeps read W in its own type)
+  if (need_grad && !t.stored && a.w_bf16 == nullptr) return ESEP_ERR_BAD_ARG;
   if (a.workspace == nullptr || (reinterpret_cast<uintptr_t>(a.workspace) & (kAlign - 1)) ||
       a.workspace_bytes < t.total)
     return ESEP_ERR_WORKSPACE;
@@ -1657,6 +1659,16 @@ int esep_weight_exact(const void* w16, int64_t v, int64_t h, int64_t count,
     g_launches.fetch_add(1);
   }
   return ESEP_OK;
+}
+
+int esep_head_step_uses_stored_logits(int64_t m, int64_t h, int64_t v, int dtype, int need_grad) {
+  if (m <= 0 || h <= 0 || v <= 0 || h % 8 != 0) return 0;
+  if (dtype != ESEP_DTYPE_F16 && dtype != ESEP_DTYPE_BF16) return 0;
+  const DeviceInfo* d = nullptr;
+  if (current_device_info(&d) != ESEP_OK) return 0;
+  StepLayout t;
+  if (step_layout(m, h, v, need_grad != 0, d, &t) != ESEP_OK) return 0;
+  return t.stored ? 1 : 0;
 }
 
 int esep_head_step_path_taken(const void* workspace, void* stream, int* out_stored) {

@@ -86,6 +86,7 @@ SIGNATURES = {
     "esep_head_debug_counters": (_INT, [ctypes.POINTER(ctypes.c_longlong), _INT]),
     "esep_head_set_training_path": (_INT, [_INT]),
     "esep_head_step_path_taken": (_INT, [_P, _P, ctypes.POINTER(_INT)]),
+    "esep_head_step_uses_stored_logits": (_INT, [_I64, _I64, _I64, _INT, _INT]),
     "esep_head_norm_forward": (_INT, [_P, _P, _P, _I64, _I64, ctypes.c_float, _INT, _P, _P, _P,
                                       _P]),
     "esep_head_norm_backward": (_INT, [_P, _P, _P, _P, _P, _I64, _I64, _INT, _P, _P, _P]),

@@ -220,10 +220,10 @@ TRAINING_PATHS = {"auto": 0, "single_pass": 1, "stored_logits": 2}
 
 def set_training_path(path="auto"):
     """Which kernels a call with gradient uses for the rows that need one (process-wide; see
-    ``esep_head_set_training_path`` in include/esep_head.h): "single_pass" keeps the logits on the
-    SM, "stored_logits" keeps them in the workspace as fp16 for a second sweep, "auto" (default)
-    takes the two sweeps where the single pass would need several passes over the hidden dimension
-    (hidden > 1536). Returns the previous setting's name."""
+    ``esep_head_set_training_path`` in include/esep_head.h): "stored_logits" keeps the logits in
+    the workspace as fp16 between a forward sweep and a dHidden sweep (the faster path on B200),
+    "single_pass" keeps them on the SM (no logits buffer), "auto" (default) takes the two sweeps
+    wherever they apply. Returns the previous setting's name."""
     prev = _lib.load().esep_head_set_training_path(TRAINING_PATHS[path])
     if prev < 0:
         _lib.check("esep_head_set_training_path", prev)
@@ -333,7 +333,9 @@ def _run_step(x, w16, need_grad, target=None, ce_weight=None, labels=None, atten
                "argmax": torch.empty(m, device=dev, dtype=torch.int64),
                "dx": torch.empty(m, h, device=dev, dtype=torch.float32) if need_grad else None}
         overflow = ws[96:100].view(torch.int32)
-        if need_grad and w_bf16 is None:
+        # only the single pass reads a bf16 copy of W (467 MB for the 1.5B shape)
+        if need_grad and w_bf16 is None and not lib.esep_head_step_uses_stored_logits(
+                m, h, v, dtype, 1):
             w_bf16 = _bf16_weight(w16)
         code = lib.esep_head_step(
             _ptr(x), _X_DTYPES[x.dtype], _ptr(w16), _ptr(w_bf16), dtype, m, h, v, _ptr(target),

@@ -193,8 +193,8 @@ size_t esep_head_step_workspace_bytes(int64_t m, int64_t h, int64_t v, int dtype
  *     than -100, a row is selected when it is attended or has a target; rows that are not
  *     selected get 0 in every output (ce / entropy are then the [B, T] per-token loss / entropy).
  * x is [m, h] in W's 16-bit type (x_dtype == dtype) or fp32 (x_dtype == ESEP_DTYPE_F32, cast
- * inside). w_bf16: a bf16 copy of W for the dHidden GEMM (pass w itself for bf16 models; may be
- * NULL when need_grad == 0). metrics[ESEP_STEP_SCALARS], overflow and top_logit[m] (the largest
+ * inside). w_bf16: a bf16 copy of W for the dHidden GEMM of the single pass (pass w itself for
+ * bf16 models; may be NULL when need_grad == 0 or when esep_head_step_uses_stored_logits says 1). metrics[ESEP_STEP_SCALARS], overflow and top_logit[m] (the largest
  * logit of every selected row, exact) may be NULL.
  * overflow: device int, 1 if a row's largest logit lay more than 115 above its maximum over the
  * first 2048 vocabulary rows; the two-kernel path (esep_head_forward + esep_head_backward), which
@@ -309,6 +309,11 @@ int esep_weight_exact(const void* w16, int64_t v, int64_t h, int64_t count,
  * workspace. Returns the previous value, or ESEP_ERR_BAD_ARG. No
  * counterpart in the reference (its chunk loop is one path). */
 int esep_head_set_training_path(int path);
+
+/* 1 when a step of this shape will take the two sweeps under the current setting (host-side
+ * decision, no launch). A caller with an fp16 model needs the bf16 copy of W (`w_bf16` of
+ * esep_head_step) only when this is 0; on the two-sweep path `w_bf16` may be NULL. */
+int esep_head_step_uses_stored_logits(int64_t m, int64_t h, int64_t v, int dtype, int need_grad);
 
 /* Which of the two the most recent esep_head_step on this workspace took (*out_stored = 1: two
  * sweeps). Synchronises the stream (a test / monitoring aid). */

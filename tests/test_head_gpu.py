@@ -737,7 +737,7 @@ def test_single_sweep_and_two_kernel_path_agree(dtype):
     check_against_oracle(x, w, t, c, loss2, stats2, dx2)
 
 
-def test_train_entry_point_rejects_bad_arguments_and_reports_its_workspace():
+def test_train_entry_point_rejects_bad_arguments_and_reports_its_workspace(training_path):
     """esep_head_train through the C ABI: workspace query, argument checks, no launch on error."""
     import ctypes
 
@@ -769,7 +769,10 @@ def test_train_entry_point_rejects_bad_arguments_and_reports_its_workspace():
                                        P(lse), P(tl), P(ce), P(ent), P(am), P(cew), P(loss), P(met),
                                        P(dx), flag_ptr, P(ws), ws_bytes, st)
 
-        assert call(wb_ptr=None) == _lib.ERR_BAD_ARG
+        # the bf16 copy of W is read by the single pass only
+        uses_stored = lib.esep_head_step_uses_stored_logits(n, h, v, _lib.DTYPE_F16, 1)
+        assert uses_stored == (1 if training_path == "two_sweeps" else 0)
+        assert call(wb_ptr=None) == (0 if uses_stored else _lib.ERR_BAD_ARG)
         assert call(flag_ptr=None) == _lib.ERR_BAD_ARG
         assert call(ws_bytes=need - 256) == _lib.ERR_WORKSPACE
         assert call() == 0
