@@ -256,6 +256,9 @@ def run_ours(args):
     from esep_soup_kernels_b200.head.synthetic import (QWEN_1P5B, QWEN_7B, make_config,
                                                        make_weight)
 
+    path_names = {0: "auto", 1: "single_pass", 2: "stored_logits"}
+    head_op.set_training_path(path_names[args.path])   # 0 unless a profile capture asks otherwise
+
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -437,7 +440,7 @@ def run_ours(args):
         try:
             ms_single = timed(step_device, 10, 3)
         finally:
-            head_op.set_training_path("auto")
+            head_op.set_training_path(path_names[args.path])
         single_tf = f_alg / (ms_single * 1e-3) / 1e12
         line_extra["single_pass_path"] = {
             "ms_per_step": ms_single, "achieved_tflops": single_tf,
@@ -773,7 +776,7 @@ def main():
     ap.add_argument("--weight-bandwidth", nargs=3, type=int, metavar=("VOCAB", "HIDDEN", "LOOKUPS"),
                     help="instead of the head: time the kernels of the shared fp16 weight format")
     ap.add_argument("--path", type=int, default=0, choices=[0, 1, 2],
-                    help="with --shape: training path (esep_head_set_training_path): 0 auto, "
+                    help="training path (esep_head_set_training_path): 0 auto (the default), "
                          "1 single pass, 2 two sweeps over stored logits")
     ap.add_argument("--shape", nargs=3, type=int, metavar=("ROWS", "HIDDEN", "VOCAB"),
                     help="instead of configuration 2: time the head step (bf16) on this shape")
