@@ -53,9 +53,9 @@ static constexpr int SLICE = 512;         // hidden columns per unit (256 per CT
 static constexpr int BLK_V = 128;         // vocabulary entries per step
 static constexpr int KV = 32;             // vocabulary rows per W slot
 static constexpr int P_SLOT = 128 * BLK_V * 2;      // 32 KiB: this CTA's rows x one step
-static constexpr int P_SLOTS = 3;
+static constexpr int P_SLOTS = 4;
 static constexpr int W_SLOT = KV * 256 * 2;         // 16 KiB
-static constexpr int W_SLOTS = 8;
+static constexpr int W_SLOTS = 6;
 static constexpr int T_WARPS = 16;                  // transform warps
 static constexpr int THREADS = 23 * 32;              // 736: see the warp roles
 static constexpr int NUM_BARS = 2 * W_SLOTS + 2 * P_SLOTS + 4;
