@@ -256,7 +256,7 @@ def run_ours(args):
     from esep_soup_kernels_b200.head.synthetic import (QWEN_1P5B, QWEN_7B, make_config,
                                                        make_weight)
 
-    path_names = {0: "auto", 1: "single_pass", 2: "stored_logits"}
+    path_names = {0: "auto", 1: "single_pass", 2: "stored_logits", 3: "stored_weights"}
     head_op.set_training_path(path_names[args.path])   # 0 unless a profile capture asks otherwise
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -775,7 +775,7 @@ def main():
                     help="instead of the head: time the final-norm kernels on ROWS x HIDDEN")
     ap.add_argument("--weight-bandwidth", nargs=3, type=int, metavar=("VOCAB", "HIDDEN", "LOOKUPS"),
                     help="instead of the head: time the kernels of the shared fp16 weight format")
-    ap.add_argument("--path", type=int, default=0, choices=[0, 1, 2],
+    ap.add_argument("--path", type=int, default=0, choices=[0, 1, 2, 3],
                     help="training path (esep_head_set_training_path): 0 auto (the default), "
                          "1 single pass, 2 two sweeps over stored logits")
     ap.add_argument("--shape", nargs=3, type=int, metavar=("ROWS", "HIDDEN", "VOCAB"),

@@ -181,9 +181,15 @@ bool init_device(int device) {
                              dxk::SMEM_BYTES) == cudaSuccess &&
         cudaFuncSetAttribute(head_dx_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              dxk::SMEM_BYTES) == cudaSuccess &&
-        cudaFuncSetAttribute(head_fwd_kernel<0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaFuncSetAttribute(head_dx_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             dxk::SMEM_BYTES) == cudaSuccess &&
+        cudaFuncSetAttribute(head_fwd_kernel<0, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              fwd::SMEM_BYTES) == cudaSuccess &&
-        cudaFuncSetAttribute(head_fwd_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaFuncSetAttribute(head_fwd_kernel<1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             fwd::SMEM_BYTES) == cudaSuccess &&
+        cudaFuncSetAttribute(head_fwd_kernel<0, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             fwd::SMEM_BYTES) == cudaSuccess &&
+        cudaFuncSetAttribute(head_fwd_kernel<1, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              fwd::SMEM_BYTES) == cudaSuccess &&
         cudaOccupancyMaxActiveClusters(&npairs, head_dx_kernel<0>, &cfg) == cudaSuccess &&
         npairs > 0)
@@ -894,6 +900,7 @@ struct StepLayout {
   int rows_nhb;        // accumulator blocks per quarter of a pass, as the row-finish kernel sees it
   int pass_w;          // columns per pass = row stride of the partial dHidden pieces
   bool stored;         // two sweeps: forward sweep that stores the logits, then head_dx_kernel
+  bool direct;         // ... stores the softmax weights themselves (bf16), head_dx_kernel<.., true>
   size_t zpitch;       // elements per row of the stored logits
   size_t z_off, c2_off, partg_off, pieces_off;
   int part_cap;        // rows of the forward partial arrays
@@ -932,7 +939,7 @@ int step_layout(int64_t m, int64_t h, int64_t v, bool need_grad, const DeviceInf
     t->ncl = static_cast<int>(
         std::min<int64_t>(d->max_clusters_wide, n_tp * pl.bwd_total_steps));
   }
-  t->stored = false;
+  t->stored = t->direct = false;
   t->zpitch = static_cast<size_t>(pl.fwd_vocab_tiles) * 256;
   {
     const int path = g_training_path.load();
@@ -944,6 +951,7 @@ int step_layout(int64_t m, int64_t h, int64_t v, bool need_grad, const DeviceInf
     if (need_grad && path != 1 && d->max_pairs_dx > 0 && h % 64 == 0 &&
         zbytes <= kMaxStoredLogitsBytes)
       t->stored = true;
+    t->direct = t->stored && path == 3;
   }
   const size_t mr = static_cast<size_t>(div_up(m, 256)) * 256;
   // Rows of the forward partial arrays: room for 16 vocabulary runs per row (the split search of
@@ -982,6 +990,8 @@ int step_layout(int64_t m, int64_t h, int64_t v, bool need_grad, const DeviceInf
     t->lo_stride = align_up(static_cast<size_t>(16) * 128 * t->ncl * f4);
     t->lo_off = take(4 * t->lo_stride);
     t->dxpart_off = take(static_cast<size_t>(t->ncl) * 128 * t->pass_w * f4);
+  }
+  if (need_grad && (!t->stored || t->direct)) {   // what the guarded second attempt leaves
     t->dxc_off = take(static_cast<size_t>(m) * h * f4);
     t->fb_stride = align_up(static_cast<size_t>(m) * f4);
     t->fb_off = take(5 * t->fb_stride);
@@ -1068,7 +1078,8 @@ int step_impl(const StepArgs& a) {
   st = step_layout(a.m, a.h, a.v, need_grad, d, &t);
   if (st != ESEP_OK) return st;
   // the bf16 copy of W is read by the single pass only (the two sweeps read W in its own type)
-  if (need_grad && !t.stored && a.w_bf16 == nullptr) return ESEP_ERR_BAD_ARG;
+  if (need_grad && (!t.stored || (t.direct && a.dtype == ESEP_DTYPE_F16)) && a.w_bf16 == nullptr)
+    return ESEP_ERR_BAD_ARG;
   if (a.workspace == nullptr || (reinterpret_cast<uintptr_t>(a.workspace) & (kAlign - 1)) ||
       a.workspace_bytes < t.total)
     return ESEP_ERR_WORKSPACE;
@@ -1171,11 +1182,18 @@ int step_impl(const StepArgs& a) {
     g.zbuf = reinterpret_cast<__half*>(ws + t.z_off);
     g.zpitch = static_cast<long long>(t.zpitch);
     g.m_ref = record;
-    st = a.dtype == ESEP_DTYPE_F16
-             ? launch_cluster(head_fwd_kernel<0, true>, fwd_grid, fwd::THREADS, fwd::SMEM_BYTES, 2,
-                              s, tx, tw, g)
-             : launch_cluster(head_fwd_kernel<1, true>, fwd_grid, fwd::THREADS, fwd::SMEM_BYTES, 2,
-                              s, tx, tw, g);
+    if (t.direct)
+      st = a.dtype == ESEP_DTYPE_F16
+               ? launch_cluster(head_fwd_kernel<0, 2>, fwd_grid, fwd::THREADS, fwd::SMEM_BYTES, 2,
+                                s, tx, tw, g)
+               : launch_cluster(head_fwd_kernel<1, 2>, fwd_grid, fwd::THREADS, fwd::SMEM_BYTES, 2,
+                                s, tx, tw, g);
+    else
+      st = a.dtype == ESEP_DTYPE_F16
+               ? launch_cluster(head_fwd_kernel<0, 1>, fwd_grid, fwd::THREADS, fwd::SMEM_BYTES, 2,
+                                s, tx, tw, g)
+               : launch_cluster(head_fwd_kernel<1, 1>, fwd_grid, fwd::THREADS, fwd::SMEM_BYTES, 2,
+                                s, tx, tw, g);
     if (st != ESEP_OK) return st;
     // 4b. per-row constant of the softmax weights, 4c. dHidden from the stored logits
     float* kexp = reinterpret_cast<float*>(ws + t.c2_off);
@@ -1183,11 +1201,21 @@ int step_impl(const StepArgs& a) {
     const unsigned rc_grid = static_cast<unsigned>(div_up(m, 128));
     head_dx_rowconst_kernel<<<rc_grid, 128, 0, s>>>(m, counts + CNT_STORE, pl.fwd_vocab_tiles,
                                                     static_cast<int>(fwd_grid / 2), t.part_cap, g.pm,
-                                                    g.ps, g.ptz, tgt_c, v, record, kexp, rscale);
+                                                    g.ps, g.ptz, tgt_c, v, record, kexp, rscale,
+                                                    t.direct ? 1 : 0, overflow);
     if (cudaGetLastError() != cudaSuccess) return ESEP_ERR_CUDA;
     g_launches.fetch_add(1);
-    CUtensorMap tw3;
-    if (make_tmap_w3(&tw3, a.w, a.dtype, a.v, a.h, dxk::KV, 4) != ESEP_OK) return ESEP_ERR_CUDA;
+    CUtensorMap tw3, tz;
+    if (t.direct) {   // P is bf16: an fp16 model's dHidden GEMM reads the bf16 copy of W
+      const void* wb = a.dtype == ESEP_DTYPE_F16 ? a.w_bf16 : a.w;
+      if (make_tmap_w3(&tw3, wb, ESEP_DTYPE_BF16, a.v, a.h, dxk::KV, 4) != ESEP_OK)
+        return ESEP_ERR_CUDA;
+      if (make_tmap(&tz, g.zbuf, ESEP_DTYPE_BF16, a.m, t.zpitch, 64, 128) != ESEP_OK)
+        return ESEP_ERR_CUDA;
+    } else {
+      if (make_tmap_w3(&tw3, a.w, a.dtype, a.v, a.h, dxk::KV, 4) != ESEP_OK) return ESEP_ERR_CUDA;
+      tz = tw3;
+    }
     DxParams dp = {};
     dp.n = m;
     dp.h = h;
@@ -1200,11 +1228,15 @@ int step_impl(const StepArgs& a) {
     dp.pieces = reinterpret_cast<float*>(ws + t.pieces_off);
     dp.status = status;
     const unsigned dx_grid = static_cast<unsigned>(2 * d->max_pairs_dx);
-    st = a.dtype == ESEP_DTYPE_F16
-             ? launch_cluster(head_dx_kernel<0>, dx_grid, dxk::THREADS, dxk::SMEM_BYTES, 2, s, tw3,
-                              dp)
-             : launch_cluster(head_dx_kernel<1>, dx_grid, dxk::THREADS, dxk::SMEM_BYTES, 2, s, tw3,
-                              dp);
+    if (t.direct)
+      st = launch_cluster(head_dx_kernel<1, true>, dx_grid, dxk::THREADS, dxk::SMEM_BYTES, 2, s,
+                          tw3, tz, dp);
+    else
+      st = a.dtype == ESEP_DTYPE_F16
+               ? launch_cluster(head_dx_kernel<0>, dx_grid, dxk::THREADS, dxk::SMEM_BYTES, 2, s,
+                                tw3, tz, dp)
+               : launch_cluster(head_dx_kernel<1>, dx_grid, dxk::THREADS, dxk::SMEM_BYTES, 2, s,
+                                tw3, tz, dp);
     if (st != ESEP_OK) return st;
     g_dx_launches.fetch_add(1);
   }
@@ -1321,7 +1353,7 @@ int step_impl(const StepArgs& a) {
   float* fb = reinterpret_cast<float*>(ws + t.fb_off);
   const size_t fbs = t.fb_stride / sizeof(float);
   long long* fb_amax = reinterpret_cast<long long*>(ws + t.fbam_off);
-  if (need_grad && !t.stored) {
+  if (need_grad && (!t.stored || t.direct)) {
     // 6. guarded second attempt on the compact rows: the two-kernel path, enqueued behind the
     //    overflow flag. Its kernels return at once unless a row overflowed in the sweep; if one
     //    did, they leave per-row results and final dHidden rows in compact order.
@@ -1668,7 +1700,7 @@ int esep_head_step_uses_stored_logits(int64_t m, int64_t h, int64_t v, int dtype
   if (current_device_info(&d) != ESEP_OK) return 0;
   StepLayout t;
   if (step_layout(m, h, v, need_grad != 0, d, &t) != ESEP_OK) return 0;
-  return t.stored ? 1 : 0;
+  return t.stored ? (t.direct ? 2 : 1) : 0;
 }
 
 int esep_head_step_path_taken(const void* workspace, void* stream, int* out_stored) {
@@ -1687,7 +1719,7 @@ int esep_head_step_path_taken(const void* workspace, void* stream, int* out_stor
 }
 
 int esep_head_set_training_path(int path) {
-  if (path < 0 || path > 2) return ESEP_ERR_BAD_ARG;
+  if (path < 0 || path > 3) return ESEP_ERR_BAD_ARG;
   return g_training_path.exchange(path);
 }
 

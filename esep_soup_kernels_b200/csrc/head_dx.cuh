@@ -62,6 +62,7 @@ static constexpr int NUM_BARS = 2 * W_SLOTS + 2 * P_SLOTS + 4;
 static constexpr int SMEM_BYTES =
     1024 + P_SLOTS * P_SLOT + W_SLOTS * W_SLOT + NUM_BARS * 8 + 64 + 128 * 8;
 static constexpr float FP16_SCALE_LOG2 = 10.f;      // P x 1024 (the reference's G_SCALE)
+static constexpr float DIRECT_OVERFLOW_NATS = 75.f; // largest z - m_ref whose weight bf16 is trusted with
 }  // namespace dxk
 
 // How the units of a launch are cut and handed out; the same on the host (buffer sizes), in the
@@ -117,9 +118,13 @@ struct DxParams {
   int* status;
 };
 
-template <int kFmt>   // type of W and of P: 0 = fp16, 1 = bf16
+// kDirect: the buffer already holds the softmax weights as bf16 (the forward sweep's second store
+// mode); a producer warp brings their tiles in by TMA, in the layout the MMAs read, and no warp
+// transforms anything. W is then a bf16 tensor whatever the model's type (kFmt = 1).
+template <int kFmt, bool kDirect = false>   // type of W and of P: 0 = fp16, 1 = bf16
 __global__ void __launch_bounds__(dxk::THREADS, 1)
 head_dx_kernel(const __grid_constant__ CUtensorMap tmap_w,   // W as {64 h, v, h/64}, box {64, 32, 4}
+               const __grid_constant__ CUtensorMap tmap_z,   // kDirect: weights [n, zpitch], box {64, 128}
                const DxParams p) {
   using namespace dxk;
   if (min(*p.n_dev, p.n) <= 0) return;   // no rows on this path (every CTA reads the same count)
@@ -162,7 +167,8 @@ head_dx_kernel(const __grid_constant__ CUtensorMap tmap_w,   // W as {64 h, v, h
       mbar_init(w_empty(s), 1);
     }
     for (uint32_t s = 0; s < P_SLOTS; ++s) {
-      mbar_init(p_ready(s), 2);             // the relay warps of both CTAs (leader's barrier)
+      // the relay warps of both CTAs, or the leader's expect-tx for both CTAs' tiles
+      mbar_init(p_ready(s), kDirect ? 1 : 2);
       p_cnt[s] = 0;
       mbar_init(p_empty(s), 1);
     }
@@ -174,6 +180,7 @@ head_dx_kernel(const __grid_constant__ CUtensorMap tmap_w,   // W as {64 h, v, h
     fence_barrier_init();
     fence_proxy_async();
     tma_prefetch_desc(&tmap_w);
+    if (kDirect) tma_prefetch_desc(&tmap_z);
   }
   if (warp == 1) {
     tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
@@ -283,10 +290,40 @@ head_dx_kernel(const __grid_constant__ CUtensorMap tmap_w,   // W as {64 h, v, h
         atomicCAS(p.status, DEV_OK, DEV_TIMEOUT_DX_MMA);
       }
     }
+  } else if (kDirect && warp == 18) {
+    // ------------------- TMA producer of P (both CTAs; this warp drains nothing) ----------
+    const bool elected = elect_one_sync();
+    uint32_t ps = 0, pph = 0;
+    bool ok = true;
+    const uint32_t p_ready_leader0 = mapa_shared(p_ready(0), 0);
+    for (int w = pair_id; w < sp.runs && ok; w += n_pairs) {
+      const int row0 = run_rp(w) * ROWS + static_cast<int>(c) * 128;
+      int s0, s1;
+      run_steps(w, s0, s1);
+      for (int st = s0; st < s1 && ok; ++st) {
+        ok = mbar_wait_warp<true>(p_empty(ps), pph ^ 1u, abort_flag);
+        if (!ok) break;
+        if (elected) {
+          if (is_leader) mbar_expect_tx(p_ready(ps), 2 * P_SLOT);
+          const uint32_t dst = p_base + ps * P_SLOT;
+          tma_load_2d_pair(dst, &tmap_z, p_ready_leader0 + 8u * ps, st * BLK_V, row0);
+          tma_load_2d_pair(dst + P_SLOT / 2, &tmap_z, p_ready_leader0 + 8u * ps, st * BLK_V + 64,
+                           row0);
+        }
+        if (++ps == P_SLOTS) {
+          ps = 0;
+          pph ^= 1u;
+        }
+      }
+    }
+    if (!ok && elected) {
+      *abort_flag = 1;
+      atomicCAS(p.status, DEV_OK, DEV_TIMEOUT_DX_PRODUCER);
+    }
   } else {
     // ------------------- transform warps: logits -> P; drain at the end of a run ----------
     const int quad = warp & 3;                  // TMEM lane quadrant this warp may read
-    const bool does_transform = quad != 1;
+    const bool does_transform = !kDirect && quad != 1;
     const int tt = ((warp - 2) - ((warp - 1) >> 2)) * 32 + lane;   // 0..511 among the transformers
     // which 128 of the 512 accumulator columns this warp drains (four warps per quadrant do)
     const int part = quad < 2 ? (warp >> 2) - 1 : (warp >> 2);
@@ -307,7 +344,7 @@ head_dx_kernel(const __grid_constant__ CUtensorMap tmap_w,   // W as {64 h, v, h
       const int row0 = run_rp(w) * ROWS + static_cast<int>(c) * 128;
       int s0, s1;
       run_steps(w, s0, s1);
-      if (warp == 5) {
+      if (!kDirect && warp == 5) {
         // ---- relay: when all sixteen transform warps have finished a slot, tell the leader.
         // This warp has no loads in flight, so its arrive does not wait for any.
         for (int st = s0; st < s1 && ok; ++st) {
@@ -480,7 +517,7 @@ head_dx_rowconst_kernel(int n_cap, const int* __restrict__ n_dev, int n_vtiles, 
                         int part_cap, const float* __restrict__ pm, const float* __restrict__ ps,
                         const float* __restrict__ ptz, const long long* __restrict__ target, int v,
                         const float* __restrict__ m_ref, float* __restrict__ kexp,
-                        float* __restrict__ rscale) {
+                        float* __restrict__ rscale, int direct, int* __restrict__ overflow) {
   const int n_rows = min(*n_dev, n_cap);
   const int row = blockIdx.x * 128 + threadIdx.x;
   if (row >= n_rows) return;
@@ -497,6 +534,15 @@ head_dx_rowconst_kernel(int n_cap, const int* __restrict__ n_dev, int n_vtiles, 
   if (t >= 0 && t < v) s += __expf(tz - m);
   const float lse = m + logf(s);
   const float c = fmaxf((m_ref[row] - lse) * LOG2E, -30000.f);
+  if (direct) {
+    // The buffer holds 2^d as bf16: the whole factor is applied by the row finish. A row whose
+    // largest logit is so far above m_ref that bf16 may not hold its weights sends the call to the
+    // guarded second attempt, as in the single pass.
+    kexp[row] = 0.f;
+    rscale[row] = exp2f(c);
+    if (!(m - m_ref[row] <= dxk::DIRECT_OVERFLOW_NATS)) *overflow = 1;
+    return;
+  }
   const float ki = rintf(c);
   kexp[row] = ki + dxk::FP16_SCALE_LOG2;
   rscale[row] = exp2f(c - ki - dxk::FP16_SCALE_LOG2);

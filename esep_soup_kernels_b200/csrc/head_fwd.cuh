@@ -22,6 +22,7 @@
 // of tile k.
 #pragma once
 
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 #include "sm100_ptx.cuh"
@@ -69,6 +70,9 @@ struct FwdParams {
   // zbuf[row - row_range[0]][vocab] = fp16((logit - m_ref[row]) * log2 e) with `zpitch` elements per row
   // (a multiple of 256, so that whole tiles can be stored); the row sums then leave the
   // target's own entry out, as the training sweeps do (it is added in fp32 by the row finish).
+  // kStore == 2 keeps the softmax weights themselves instead: bf16(2^((logit - m_ref) log2 e)),
+  // zero at the target's entry and past the end of the vocabulary, so that the dHidden kernel can
+  // take its tiles straight from this buffer (bf16 has fp32's exponent range: see m_ref's margin).
   __half* zbuf;
   long long zpitch;
   const float* m_ref;
@@ -190,7 +194,7 @@ __device__ __forceinline__ void fold_chunk(RowState& st, const uint32_t (&r)[32]
   }
 }
 
-template <int kFmt, bool kStore = false>  // kFmt: 0 = fp16, 1 = bf16
+template <int kFmt, int kStore = 0>  // kFmt: 0 = fp16, 1 = bf16; kStore: 0 none, 1 logits, 2 weights
 __global__ void __launch_bounds__(fwd::THREADS, 1)
 head_fwd_kernel(const __grid_constant__ CUtensorMap tmap_x,
                 const __grid_constant__ CUtensorMap tmap_w, const FwdParams p) {
@@ -386,7 +390,33 @@ head_fwd_kernel(const __grid_constant__ CUtensorMap tmap_x,
           tmem_ld32(taddr + c * 32, r);
           tmem_ld_wait();
           const int nvalid = tile_valid - c * 32;
-          if (kStore && zrow != nullptr) {
+          if (kStore == 2 && zrow != nullptr) {
+            // 32 softmax weights of this row relative to its reference maximum, as bf16
+            uint32_t hw[16];
+            const float mref2 = mref * LOG2E;
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+              const __nv_bfloat162 hv = __floats2bfloat162_rn(
+                  ex2_approx(fmaf(__uint_as_float(r[2 * e]), LOG2E, -mref2)),
+                  ex2_approx(fmaf(__uint_as_float(r[2 * e + 1]), LOG2E, -mref2)));
+              hw[e] = *reinterpret_cast<const uint32_t*>(&hv);
+            }
+            // entries that must read as zero: the target's (added in fp32 by the row finish) and
+            // those past the end of the vocabulary
+            const unsigned tl = static_cast<unsigned>(tgt_local - (v0 + c * 32));
+            uint32_t keep = nvalid >= 32 ? 0xffffffffu : (nvalid <= 0 ? 0u : ((1u << nvalid) - 1u));
+            if (tl < 32u) keep &= ~(1u << tl);
+            if (keep != 0xffffffffu) {
+#pragma unroll
+              for (int e = 0; e < 16; ++e)
+                hw[e] &= (((keep >> (2 * e)) & 1u) ? 0x0000ffffu : 0u) |
+                         (((keep >> (2 * e + 1)) & 1u) ? 0xffff0000u : 0u);
+            }
+            uint4* dst = reinterpret_cast<uint4*>(zrow + v0 + c * 32);
+#pragma unroll
+            for (int g = 0; g < 4; ++g)
+              dst[g] = make_uint4(hw[4 * g], hw[4 * g + 1], hw[4 * g + 2], hw[4 * g + 3]);
+          } else if (kStore == 1 && zrow != nullptr) {
             // 32 logits of this row, relative to its reference maximum and in units of ln 2, as 64
             // bytes of fp16 (the dHidden kernel's 2^x takes them as they are)
             uint4* dst = reinterpret_cast<uint4*>(zrow + v0 + c * 32);
@@ -403,7 +433,7 @@ head_fwd_kernel(const __grid_constant__ CUtensorMap tmap_x,
               dst[g] = make_uint4(hw[0], hw[1], hw[2], hw[3]);
             }
           }
-          if (nvalid > 0) fold_chunk<kStore>(st, r, v0 + c * 32, nvalid, tgt_local);
+          if (nvalid > 0) fold_chunk<(kStore != 0)>(st, r, v0 + c * 32, nvalid, tgt_local);
         }
         tc_fence_before();
         __syncwarp();

@@ -215,7 +215,7 @@ class DeviceBackend:
         return dx
 
 
-TRAINING_PATHS = {"auto": 0, "single_pass": 1, "stored_logits": 2}
+TRAINING_PATHS = {"auto": 0, "single_pass": 1, "stored_logits": 2, "stored_weights": 3}
 
 
 def set_training_path(path="auto"):
@@ -333,10 +333,12 @@ def _run_step(x, w16, need_grad, target=None, ce_weight=None, labels=None, atten
                "argmax": torch.empty(m, device=dev, dtype=torch.int64),
                "dx": torch.empty(m, h, device=dev, dtype=torch.float32) if need_grad else None}
         overflow = ws[96:100].view(torch.int32)
-        # only the single pass reads a bf16 copy of W (467 MB for the 1.5B shape)
-        if need_grad and w_bf16 is None and not lib.esep_head_step_uses_stored_logits(
-                m, h, v, dtype, 1):
-            w_bf16 = _bf16_weight(w16)
+        # a bf16 copy of W (467 MB for the 1.5B shape) is read by the single pass (0) and, for an
+        # fp16 model, by the two sweeps that keep bf16 softmax weights (2)
+        if need_grad and w_bf16 is None:
+            kind = lib.esep_head_step_uses_stored_logits(m, h, v, dtype, 1)
+            if kind == 0 or (kind == 2 and w16.dtype == torch.float16):
+                w_bf16 = _bf16_weight(w16)
         code = lib.esep_head_step(
             _ptr(x), _X_DTYPES[x.dtype], _ptr(w16), _ptr(w_bf16), dtype, m, h, v, _ptr(target),
             _ptr(ce_weight), _ptr(labels), _ptr(attention_mask), int(seq_len), int(need_grad),
