@@ -944,14 +944,14 @@ int step_layout(int64_t m, int64_t h, int64_t v, bool need_grad, const DeviceInf
   {
     const int path = g_training_path.load();
     const size_t zbytes = static_cast<size_t>(m) * t->zpitch * 2;
-    // Measured on B200 (same box, alternating): two sweeps 3.41 against 3.55 ms at 4 340 x 1536 x
-    // 151 936, 13.7 against 14.4 ms at 16 384 rows, 9.7 against 13.5 ms at the 7B shard shape
-    // (32 768 x 3584 x 19 008, single pass on 8-CTA clusters): they are the default wherever they
-    // apply; the single pass remains for callers that cannot spare the logits buffer (path 1).
+    // Measured on B200 (same box, alternating), 4 340 x 1536 x 151 936: single pass 3.55 ms, two
+    // sweeps over fp16 logits 3.39 ms, two sweeps over bf16 softmax weights 2.91 ms; 7B shard shape
+    // (32 768 x 3584 x 19 008): 13.5 / 8.9 - 9.4 / 7.7 - 8.7 ms. The two sweeps are the default
+    // wherever they apply; the single pass remains for callers that cannot spare the buffer.
     if (need_grad && path != 1 && d->max_pairs_dx > 0 && h % 64 == 0 &&
         zbytes <= kMaxStoredLogitsBytes)
       t->stored = true;
-    t->direct = t->stored && path == 3;
+    t->direct = t->stored && path != 2;   // path 2: fp16 logits, transformed by the dHidden kernel
   }
   const size_t mr = static_cast<size_t>(div_up(m, 256)) * 256;
   // Rows of the forward partial arrays: room for 16 vocabulary runs per row (the split search of

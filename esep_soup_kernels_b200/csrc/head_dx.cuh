@@ -38,6 +38,7 @@
 #include <algorithm>
 
 #include "head_bwd.cuh"
+#include "head_fwd.cuh"
 
 namespace esep {
 
@@ -533,16 +534,18 @@ head_dx_rowconst_kernel(int n_cap, const int* __restrict__ n_dev, int n_vtiles, 
   const long long t = target[row];
   if (t >= 0 && t < v) s += __expf(tz - m);
   const float lse = m + logf(s);
-  const float c = fmaxf((m_ref[row] - lse) * LOG2E, -30000.f);
   if (direct) {
+    const float ref = m_ref[row] + fwd::STORED_WEIGHT_MARGIN;
+    const float c = fmaxf((ref - lse) * LOG2E, -30000.f);
     // The buffer holds 2^d as bf16: the whole factor is applied by the row finish. A row whose
     // largest logit is so far above m_ref that bf16 may not hold its weights sends the call to the
     // guarded second attempt, as in the single pass.
     kexp[row] = 0.f;
     rscale[row] = exp2f(c);
-    if (!(m - m_ref[row] <= dxk::DIRECT_OVERFLOW_NATS)) *overflow = 1;
+    if (!(m - ref <= dxk::DIRECT_OVERFLOW_NATS)) *overflow = 1;
     return;
   }
+  const float c = fmaxf((m_ref[row] - lse) * LOG2E, -30000.f);
   const float ki = rintf(c);
   kexp[row] = ki + dxk::FP16_SCALE_LOG2;
   rscale[row] = exp2f(c - ki - dxk::FP16_SCALE_LOG2);

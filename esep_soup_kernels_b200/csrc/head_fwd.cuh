@@ -70,7 +70,7 @@ struct FwdParams {
   // zbuf[row - row_range[0]][vocab] = fp16((logit - m_ref[row]) * log2 e) with `zpitch` elements per row
   // (a multiple of 256, so that whole tiles can be stored); the row sums then leave the
   // target's own entry out, as the training sweeps do (it is added in fp32 by the row finish).
-  // kStore == 2 keeps the softmax weights themselves instead: bf16(2^((logit - m_ref) log2 e)),
+  // kStore == 2 keeps the softmax weights themselves instead: bf16(2^((logit - m_ref - 40) log2 e)),
   // zero at the target's entry and past the end of the vocabulary, so that the dHidden kernel can
   // take its tiles straight from this buffer (bf16 has fp32's exponent range: see m_ref's margin).
   __half* zbuf;
@@ -130,6 +130,9 @@ static constexpr int THREADS = 192;
 static constexpr int TMEM_COLS = 512;
 // barriers: full[STAGES], empty[STAGES], tfull[2], tempty[2]
 static constexpr int NUM_BARS = 2 * STAGES + 4;
+// Stored softmax weights (kStore == 2) are taken relative to m_ref + this margin: bf16 then holds
+// them for logits from 47 below to 128 above m_ref (the single pass uses the same reference).
+static constexpr float STORED_WEIGHT_MARGIN = 40.f;
 static constexpr int SMEM_BYTES = 1024 /*alignment slack*/ + STAGES * STAGE_BYTES + NUM_BARS * 8 + 64;
 }  // namespace fwd
 
@@ -393,7 +396,7 @@ head_fwd_kernel(const __grid_constant__ CUtensorMap tmap_x,
           if (kStore == 2 && zrow != nullptr) {
             // 32 softmax weights of this row relative to its reference maximum, as bf16
             uint32_t hw[16];
-            const float mref2 = mref * LOG2E;
+            const float mref2 = (mref + STORED_WEIGHT_MARGIN) * LOG2E;
 #pragma unroll
             for (int e = 0; e < 16; ++e) {
               const __nv_bfloat162 hv = __floats2bfloat162_rn(

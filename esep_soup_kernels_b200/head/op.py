@@ -220,10 +220,11 @@ TRAINING_PATHS = {"auto": 0, "single_pass": 1, "stored_logits": 2, "stored_weigh
 
 def set_training_path(path="auto"):
     """Which kernels a call with gradient uses for the rows that need one (process-wide; see
-    ``esep_head_set_training_path`` in include/esep_head.h): "stored_logits" keeps the logits in
-    the workspace as fp16 between a forward sweep and a dHidden sweep (the faster path on B200),
-    "single_pass" keeps them on the SM (no logits buffer), "auto" (default) takes the two sweeps
-    wherever they apply. Returns the previous setting's name."""
+    ``esep_head_set_training_path`` in include/esep_head.h): "stored_weights" keeps the softmax
+    weights in the workspace as bf16 between a forward sweep and a dHidden sweep (the fastest path
+    on B200), "stored_logits" keeps fp16 logits instead (no bf16 copy of an fp16 W),
+    "single_pass" keeps them on the SM (no buffer), "auto" (default) takes "stored_weights"
+    wherever the two sweeps apply. Returns the previous setting's name."""
     prev = _lib.load().esep_head_set_training_path(TRAINING_PATHS[path])
     if prev < 0:
         _lib.check("esep_head_set_training_path", prev)

@@ -194,7 +194,7 @@ size_t esep_head_step_workspace_bytes(int64_t m, int64_t h, int64_t v, int dtype
  *     selected get 0 in every output (ce / entropy are then the [B, T] per-token loss / entropy).
  * x is [m, h] in W's 16-bit type (x_dtype == dtype) or fp32 (x_dtype == ESEP_DTYPE_F32, cast
  * inside). w_bf16: a bf16 copy of W for the dHidden GEMM of the single pass (pass w itself for
- * bf16 models; may be NULL when need_grad == 0 or when esep_head_step_uses_stored_logits says 1). metrics[ESEP_STEP_SCALARS], overflow and top_logit[m] (the largest
+ * bf16 models; may be NULL when need_grad == 0 or where esep_head_step_uses_stored_logits says so). metrics[ESEP_STEP_SCALARS], overflow and top_logit[m] (the largest
  * logit of every selected row, exact) may be NULL.
  * overflow: device int, 1 if a row's largest logit lay more than 115 above its maximum over the
  * first 2048 vocabulary rows; the two-kernel path (esep_head_forward + esep_head_backward), which
@@ -299,20 +299,31 @@ int esep_weight_exact(const void* w16, int64_t v, int64_t h, int64_t count,
 /* Which kernels a call with gradient runs over the rows that need one.
  *   single pass  - head_train_kernel (8-CTA clusters at hidden 3200 - 3584): the logits never
  *                  leave the SM; smallest workspace;
- *   two sweeps   - a forward sweep that keeps (logit - reference maximum) log2 e as fp16 in the
- *                  workspace (rows x vocabulary x 2 bytes), then dHidden from those logits
- *                  (head_dx_kernel). Needs hidden % 64 == 0 and at most 48 GiB of stored logits.
- * path 0 (default) and 2: two sweeps wherever they apply (the faster path on B200 at every size
- * measured: 3.41 against 3.55 ms at 4 340 x 1536 x 151 936, 9.7 against 13.5 ms at 32 768 x 3584 x
- * 19 008), else the single pass; 1: always the single pass (no logits buffer in the workspace).
+ *   two sweeps   - a forward sweep that keeps one 16-bit value per logit in the workspace (rows x
+ *                  vocabulary x 2 bytes), then dHidden from that buffer (head_dx_kernel). Needs
+ *                  hidden % 64 == 0 and at most 48 GiB for the buffer. The value kept is either
+ *                  the softmax weight itself, bf16 2^((logit - reference) log2 e), which
+ *                  the dHidden kernel takes by TMA as it is ("stored weights"; its GEMM is bf16,
+ *                  so an fp16 model passes a bf16 copy of W; the reference is the row maximum
+ *                  over the first 2 048 vocabulary entries + 40, and a row whose maximum lies more
+ *                  than 75 above it sends the call to the guarded second attempt, as in the
+ *                  single pass), or (logit - reference maximum) log2 e as fp16, which sixteen
+ *                  warps of the dHidden kernel turn into weights ("stored logits"; no bf16 copy
+ *                  of W, no guard).
+ * path 0 (default) and 3: stored weights wherever the two sweeps apply, else the single pass;
+ * 2: stored logits wherever they apply, else the single pass; 1: always the single pass (no
+ * buffer in the workspace). Measured at 4 340 x 1536 x 151 936 on one B200: 2.91 (stored
+ * weights) / 3.39 (stored logits) / 3.55 ms (single pass); at 32 768 x 3584 x 19 008: 7.7 - 8.7 /
+ * 8.9 - 9.4 / 13.5 ms.
  * Process-wide, read when a call (or a workspace query) is made: set it before sizing the
  * workspace. Returns the previous value, or ESEP_ERR_BAD_ARG. No
  * counterpart in the reference (its chunk loop is one path). */
 int esep_head_set_training_path(int path);
 
-/* 1 when a step of this shape will take the two sweeps under the current setting (host-side
- * decision, no launch). A caller with an fp16 model needs the bf16 copy of W (`w_bf16` of
- * esep_head_step) only when this is 0; on the two-sweep path `w_bf16` may be NULL. */
+/* Which path a step of this shape will take under the current setting (host-side decision, no
+ * launch): 0 single pass, 1 two sweeps over stored logits, 2 two sweeps over stored weights. A
+ * caller with an fp16 model needs the bf16 copy of W (`w_bf16` of esep_head_step) when this is
+ * 0 or 2; when it is 1, and for bf16 models when it is 2, `w_bf16` may be NULL. */
 int esep_head_step_uses_stored_logits(int64_t m, int64_t h, int64_t v, int dtype, int need_grad);
 
 /* Which of the two the most recent esep_head_step on this workspace took (*out_stored = 1: two

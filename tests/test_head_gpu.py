@@ -14,13 +14,14 @@ from tests.helpers import check_against_oracle, run_op
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(autouse=True, params=["two_sweeps", "single_pass"])
+@pytest.fixture(autouse=True, params=["two_sweeps", "stored_logits", "single_pass"])
 def training_path(request):
-    """Every test runs on both training paths of the library: the default (two sweeps over stored
-    logits wherever they apply) and the single pass that keeps the logits on the SM."""
+    """Every test runs on the three training paths of the library: the default (two sweeps, bf16
+    softmax weights kept between them, wherever that applies), two sweeps over fp16 logits, and
+    the single pass that keeps the logits on the SM."""
     from esep_soup_kernels_b200.head.op import set_training_path
 
-    set_training_path("auto" if request.param == "two_sweeps" else "single_pass")
+    set_training_path("auto" if request.param == "two_sweeps" else request.param)
     yield request.param
     set_training_path("auto")
 
@@ -342,15 +343,17 @@ def _dx_launches():
     (2600, 704, 2100, torch.bfloat16, 5.0),    # eleven row pairs x two slices (the second ragged)
     (129, 192, 40000, torch.float16, 0.0),     # few units, long vocabulary: cut into runs
 ])
-def test_two_sweeps_over_stored_logits_match_the_oracle(n, h, v, dtype, peak):
-    """The training path that keeps the logits: forward sweep storing (logit - reference maximum)
-    log2 e as fp16, then dHidden from the stored logits (P = one packed 2^x per two entries, the
-    target's own term added in fp32). Same outputs, same tolerances, bit-identical when repeated;
+@pytest.mark.parametrize("path", ["stored_logits", "stored_weights"])
+def test_two_sweeps_over_stored_logits_match_the_oracle(n, h, v, dtype, peak, path):
+    """The training paths that keep the logits: forward sweep storing (logit - reference maximum)
+    log2 e as fp16, then dHidden from the stored logits (P = one packed 2^x per two entries), or
+    storing bf16 2^((logit - reference maximum) log2 e), which the dHidden kernel takes as it is;
+    the target's own term is added in fp32. Same outputs, same tolerances, bit-identical when repeated;
     exact zeros on rows without a loss; the library's counter shows that the kernel ran."""
     from esep_soup_kernels_b200.head.op import set_training_path
 
     x, w, t, c = _peaked(n, h, v, 1.0 / h ** 0.5, peak, n + h, dtype=dtype)
-    set_training_path("stored_logits")
+    set_training_path(path)
     try:
         before = _dx_launches()
         loss, stats, dx = run_op(x, w, t, c)
@@ -693,19 +696,24 @@ def test_single_sweep_falls_back_when_a_row_maximum_is_far_above_the_prefix():
         loss, stats, dx = run_op(x, w, t, c)
         assert not last_call_fell_back("cuda:0")
         check_against_oracle(x, w, t, c, loss, stats, dx)
-    # the same guard behind the 8-CTA-cluster sweep (hidden 3584); the two-sweep path knows the
-    # true maximum before it forms a weight and needs no guard
+    # the same guard behind the 8-CTA-cluster sweep (hidden 3584) and behind the two sweeps that
+    # keep bf16 weights relative to the same reference; the two sweeps over fp16 logits know the
+    # true maximum before they form a weight and need no guard
     x, w, t, c = _planted_outlier_case(600.0, h=3584)
-    set_training_path("single_pass")
     try:
+        for path, falls_back in (("single_pass", True), ("stored_weights", True),
+                                 ("stored_logits", False)):
+            set_training_path(path)
+            loss, stats, dx = run_op(x, w, t, c)
+            assert last_call_fell_back("cuda:0") == falls_back
+            check_against_oracle(x, w, t, c, loss, stats, dx)
+        x, w, t, c = _planted_outlier_case(150.0)
+        set_training_path("stored_weights")
         loss, stats, dx = run_op(x, w, t, c)
-        assert last_call_fell_back("cuda:0")
+        assert not last_call_fell_back("cuda:0")
         check_against_oracle(x, w, t, c, loss, stats, dx)
     finally:
         set_training_path("auto")
-    loss, stats, dx = run_op(x, w, t, c)
-    assert not last_call_fell_back("cuda:0")
-    check_against_oracle(x, w, t, c, loss, stats, dx)
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
@@ -769,10 +777,10 @@ def test_train_entry_point_rejects_bad_arguments_and_reports_its_workspace(train
                                        P(lse), P(tl), P(ce), P(ent), P(am), P(cew), P(loss), P(met),
                                        P(dx), flag_ptr, P(ws), ws_bytes, st)
 
-        # the bf16 copy of W is read by the single pass only
+        # the two sweeps over fp16 logits are the one path that reads no bf16 copy of W
         uses_stored = lib.esep_head_step_uses_stored_logits(n, h, v, _lib.DTYPE_F16, 1)
-        assert uses_stored == (1 if training_path == "two_sweeps" else 0)
-        assert call(wb_ptr=None) == (0 if uses_stored else _lib.ERR_BAD_ARG)
+        assert uses_stored == {"two_sweeps": 2, "stored_logits": 1, "single_pass": 0}[training_path]
+        assert call(wb_ptr=None) == (0 if uses_stored == 1 else _lib.ERR_BAD_ARG)
         assert call(flag_ptr=None) == _lib.ERR_BAD_ARG
         assert call(ws_bytes=need - 256) == _lib.ERR_WORKSPACE
         assert call() == 0
