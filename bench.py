@@ -482,14 +482,14 @@ def run_ours(args):
                              "NCCL's all-reduce",
         "clocks": clocks,
         "roofline": {"bound": "tensor",
-                     "kernel": "head_fwd_kernel<store> + head_dx_kernel (the two sweeps of the step: "
-                               "logits GEMM, dHidden GEMM)",
+                     "kernel": "head_fwd_kernel<store weights> + head_dx_kernel<direct> (the two "
+                               "sweeps of the step: logits GEMM, dHidden GEMM)",
                      "achieved": call_tf,
                      "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": call_tf / peaks["tflops"],
-                     "traffic": _traffic_sum("head_fwd_kernel_store", "head_dx_kernel"),
-                     "traffic_note": "DRAM bytes of the two kernels per step (ncu): the logits are "
-                                     "written once as fp16 (1.27 GB) and read by the second sweep, "
-                                     "W is read by both",
+                     "traffic": _traffic_sum("head_fwd_kernel_weights", "head_dx_kernel_weights"),
+                     "traffic_note": "DRAM bytes of the two kernels per step (ncu): the softmax "
+                                     "weights are written once as bf16 (1.28 GB) and read by the "
+                                     "second sweep, W is read by both",
                      "peak_source": peaks["source"] + " burst",
                      "flops": "algorithmic 2*H*V*N + 2*H*V*N_live (logits GEMM + dHidden GEMM, each "
                               "once), which is also what the two sweeps execute",
@@ -498,7 +498,7 @@ def run_ours(args):
                      "ms_note": "mean over the timed steps of the CUDA-event time of the whole "
                                 "esep_head_step call inside the timed loop (row classes, gather, "
                                 "prefix sweep, storing forward sweep, dHidden sweep, row finish, "
-                                "scalars); the two sweeps are 92 % of it in the ncu launch list"},
+                                "scalars); the two sweeps are 91 % of it in the ncu launch list"},
         "step_tensor_frac": f_alg / (ms_step * 1e-3) / 1e12 / peaks["tflops"],
         "device_status": status,
         "plan": {"sm_count": caps.sm_count, "bwd_clusters_resident": caps.max_clusters_bwd,
