@@ -777,7 +777,8 @@ def main():
                     help="instead of the head: time the kernels of the shared fp16 weight format")
     ap.add_argument("--path", type=int, default=0, choices=[0, 1, 2, 3],
                     help="training path (esep_head_set_training_path): 0 auto (the default), "
-                         "1 single pass, 2 two sweeps over stored logits")
+                         "1 single pass, 2 two sweeps over stored fp16 logits, 3 two sweeps over stored bf16 "
+                         "softmax weights (what 0 takes wherever the two sweeps apply)")
     ap.add_argument("--shape", nargs=3, type=int, metavar=("ROWS", "HIDDEN", "VOCAB"),
                     help="instead of configuration 2: time the head step (bf16) on this shape")
     args = ap.parse_args()

@@ -188,9 +188,9 @@ bool init_device(int device) {
         cudaFuncSetAttribute(head_fwd_kernel<1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              fwd::SMEM_BYTES) == cudaSuccess &&
         cudaFuncSetAttribute(head_fwd_kernel<0, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             fwd::SMEM_BYTES) == cudaSuccess &&
+                             fwd::SMEM_BYTES_STORE) == cudaSuccess &&
         cudaFuncSetAttribute(head_fwd_kernel<1, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             fwd::SMEM_BYTES) == cudaSuccess &&
+                             fwd::SMEM_BYTES_STORE) == cudaSuccess &&
         cudaOccupancyMaxActiveClusters(&npairs, head_dx_kernel<0>, &cfg) == cudaSuccess &&
         npairs > 0)
       d.max_pairs_dx = std::min(npairs, d.sm_count / 2);
@@ -529,8 +529,8 @@ int esep_head_forward_partial(const void* x, const void* w, const int64_t* targe
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
     const cudaError_t e = dtype == ESEP_DTYPE_F16
-                              ? cudaLaunchKernelEx(&cfg, head_fwd_kernel<0>, tx, tw, p)
-                              : cudaLaunchKernelEx(&cfg, head_fwd_kernel<1>, tx, tw, p);
+                              ? cudaLaunchKernelEx(&cfg, head_fwd_kernel<0>, tx, tw, tw, p)
+                              : cudaLaunchKernelEx(&cfg, head_fwd_kernel<1>, tx, tw, tw, p);
     if (e != cudaSuccess) {
       cudaGetLastError();
       return ESEP_ERR_CUDA;
@@ -1182,18 +1182,22 @@ int step_impl(const StepArgs& a) {
     g.zbuf = reinterpret_cast<__half*>(ws + t.z_off);
     g.zpitch = static_cast<long long>(t.zpitch);
     g.m_ref = record;
-    if (t.direct)
+    if (t.direct) {
+      CUtensorMap tzs;   // the weights buffer as the epilogue warps store it: boxes of 64 x 32 rows
+      if (make_tmap(&tzs, g.zbuf, ESEP_DTYPE_BF16, a.m, t.zpitch, 64, 32) != ESEP_OK)
+        return ESEP_ERR_CUDA;
       st = a.dtype == ESEP_DTYPE_F16
-               ? launch_cluster(head_fwd_kernel<0, 2>, fwd_grid, fwd::THREADS, fwd::SMEM_BYTES, 2,
-                                s, tx, tw, g)
-               : launch_cluster(head_fwd_kernel<1, 2>, fwd_grid, fwd::THREADS, fwd::SMEM_BYTES, 2,
-                                s, tx, tw, g);
-    else
+               ? launch_cluster(head_fwd_kernel<0, 2>, fwd_grid, fwd::THREADS,
+                                fwd::SMEM_BYTES_STORE, 2, s, tx, tw, tzs, g)
+               : launch_cluster(head_fwd_kernel<1, 2>, fwd_grid, fwd::THREADS,
+                                fwd::SMEM_BYTES_STORE, 2, s, tx, tw, tzs, g);
+    } else {
       st = a.dtype == ESEP_DTYPE_F16
                ? launch_cluster(head_fwd_kernel<0, 1>, fwd_grid, fwd::THREADS, fwd::SMEM_BYTES, 2,
-                                s, tx, tw, g)
+                                s, tx, tw, tw, g)
                : launch_cluster(head_fwd_kernel<1, 1>, fwd_grid, fwd::THREADS, fwd::SMEM_BYTES, 2,
-                                s, tx, tw, g);
+                                s, tx, tw, tw, g);
+    }
     if (st != ESEP_OK) return st;
     // 4b. per-row constant of the softmax weights, 4c. dHidden from the stored logits
     float* kexp = reinterpret_cast<float*>(ws + t.c2_off);
@@ -1344,9 +1348,9 @@ int step_impl(const StepArgs& a) {
     f.part_cap = t.part_cap;
     st = a.dtype == ESEP_DTYPE_F16
              ? launch_cluster(head_fwd_kernel<0>, fwd_grid, fwd::THREADS, fwd::SMEM_BYTES, 2, s, tx,
-                              tw, f)
+                              tw, tw, f)
              : launch_cluster(head_fwd_kernel<1>, fwd_grid, fwd::THREADS, fwd::SMEM_BYTES, 2, s, tx,
-                              tw, f);
+                              tw, tw, f);
     if (st != ESEP_OK) return st;
   }
 

@@ -134,6 +134,14 @@ static constexpr int NUM_BARS = 2 * STAGES + 4;
 // them for logits from 47 below to 128 above m_ref (the single pass uses the same reference).
 static constexpr float STORED_WEIGHT_MARGIN = 40.f;
 static constexpr int SMEM_BYTES = 1024 /*alignment slack*/ + STAGES * STAGE_BYTES + NUM_BARS * 8 + 64;
+// kStore == 2: each epilogue warp stages 32 rows x 64 weights (4 KiB, the layout of a TMA box with
+// 128-byte swizzle) in one of two buffers and stores it with one TMA instruction: whole 128-byte
+// lines reach L2 instead of one 16-byte piece per thread and instruction.
+static constexpr int ZSTAGE_OFF = STAGES * STAGE_BYTES + 1024;   // past the barriers, 1 KiB aligned
+static constexpr int ZSTAGE_BYTES = 4 * 2 * 4096;
+static constexpr int SMEM_BYTES_STORE = 1024 + ZSTAGE_OFF + ZSTAGE_BYTES;
+static_assert(NUM_BARS * 8 + 64 <= 1024, "barriers overlap the staging buffers");
+static_assert(SMEM_BYTES_STORE <= 227 * 1024, "shared memory");
 }  // namespace fwd
 
 // Folds 32 logits (one TMEM chunk of this thread's row) into the running record.
@@ -200,7 +208,9 @@ __device__ __forceinline__ void fold_chunk(RowState& st, const uint32_t (&r)[32]
 template <int kFmt, int kStore = 0>  // kFmt: 0 = fp16, 1 = bf16; kStore: 0 none, 1 logits, 2 weights
 __global__ void __launch_bounds__(fwd::THREADS, 1)
 head_fwd_kernel(const __grid_constant__ CUtensorMap tmap_x,
-                const __grid_constant__ CUtensorMap tmap_w, const FwdParams p) {
+                const __grid_constant__ CUtensorMap tmap_w,
+                const __grid_constant__ CUtensorMap tmap_z,   // kStore == 2: zbuf, box {64, 32}
+                const FwdParams p) {
   using namespace fwd;
   if (p.gate != nullptr && *p.gate == 0) return;   // guarded launch: not needed this time
   if (p.row_range != nullptr && p.row_range[1] <= p.row_range[0]) return;   // no rows to sweep
@@ -353,6 +363,8 @@ head_fwd_kernel(const __grid_constant__ CUtensorMap tmap_x,
     const int quad = warp & 3;           // TMEM lane quadrant this warp may read
     const int row_in_tile = quad * 32 + lane;
     uint32_t acc = 0, aphase = 0;
+    const uint32_t zstage = base + ZSTAGE_OFF + static_cast<uint32_t>(quad) * 8192u;
+    uint32_t zpairs = 0;                 // chunk pairs this warp has stored (buffer = zpairs & 1)
     bool ok = true;
     const uint32_t tempty_leader0 = mapa_shared(tempty_bar(0), 0);
     for (int u = pair_id; u < n_units && ok; u += n_pairs) {
@@ -372,6 +384,9 @@ head_fwd_kernel(const __grid_constant__ CUtensorMap tmap_x,
           zrow = p.zbuf + static_cast<size_t>(row - row0) * p.zpitch;
         }
       }
+      // kStore == 2: the warp stores its 32 rows together (rows past the end hold finite junk that
+      // nothing reads)
+      const bool zwarp = kStore == 2 && row0 + rt * BM + quad * 32 < row_end;
       RowState st;
       st.m = NEG_BIG;
       st.ml2 = NEG_BIG * LOG2E;
@@ -393,7 +408,7 @@ head_fwd_kernel(const __grid_constant__ CUtensorMap tmap_x,
           tmem_ld32(taddr + c * 32, r);
           tmem_ld_wait();
           const int nvalid = tile_valid - c * 32;
-          if (kStore == 2 && zrow != nullptr) {
+          if (kStore == 2 && zwarp) {
             // 32 softmax weights of this row relative to its reference maximum, as bf16
             uint32_t hw[16];
             const float mref2 = (mref + STORED_WEIGHT_MARGIN) * LOG2E;
@@ -415,10 +430,25 @@ head_fwd_kernel(const __grid_constant__ CUtensorMap tmap_x,
                 hw[e] &= (((keep >> (2 * e)) & 1u) ? 0x0000ffffu : 0u) |
                          (((keep >> (2 * e + 1)) & 1u) ? 0xffff0000u : 0u);
             }
-            uint4* dst = reinterpret_cast<uint4*>(zrow + v0 + c * 32);
+            // two chunks = one box of 64 weights x 32 rows: line = lane, 16-byte group XOR line & 7
+            const uint32_t zb = zstage + (zpairs & 1u) * 4096u;
+            if ((c & 1) == 0) {
+              if (lane == 0) bulk_wait_group_read<1>();   // the store that last read this buffer
+              __syncwarp();
+            }
 #pragma unroll
             for (int g = 0; g < 4; ++g)
-              dst[g] = make_uint4(hw[4 * g], hw[4 * g + 1], hw[4 * g + 2], hw[4 * g + 3]);
+              st_shared_v4(zb + static_cast<uint32_t>(lane * 128 + ((((c & 1) * 4 + g) ^ (lane & 7)) * 16)),
+                           hw[4 * g], hw[4 * g + 1], hw[4 * g + 2], hw[4 * g + 3]);
+            if (c & 1) {
+              fence_proxy_async_shared();
+              __syncwarp();
+              if (lane == 0) {
+                tma_store_2d(&tmap_z, zb, v0 + (c - 1) * 32, rt * BM + quad * 32);
+                bulk_commit_group();
+              }
+              ++zpairs;
+            }
           } else if (kStore == 1 && zrow != nullptr) {
             // 32 logits of this row, relative to its reference maximum and in units of ln 2, as 64
             // bytes of fp16 (the dHidden kernel's 2^x takes them as they are)
@@ -453,6 +483,7 @@ head_fwd_kernel(const __grid_constant__ CUtensorMap tmap_x,
         p.pidx[o] = st.idx;
       }
     }
+    if (kStore == 2 && lane == 0) bulk_wait_group<0>();   // this warp's stores have landed
     if (!ok && lane == 0) {
       *abort_flag = 1;
       atomicCAS(p.status, DEV_OK, DEV_TIMEOUT_EPILOGUE);
