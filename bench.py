@@ -262,8 +262,11 @@ def run_ours(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
-    if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
-        os.environ["NCCL_DEBUG"] = "WARN"      # keep NCCL's version banner off stdout: one JSON line
+    # stdout carries one JSON line: NCCL's version banner (printed from the VERSION level up) and
+    # anything else it logs go to stderr
+    if os.environ.get("NCCL_DEBUG", "").upper() in ("VERSION", "WARN"):
+        del os.environ["NCCL_DEBUG"]
+    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
@@ -498,7 +501,7 @@ def run_ours(args):
                      "ms_note": "mean over the timed steps of the CUDA-event time of the whole "
                                 "esep_head_step call inside the timed loop (row classes, gather, "
                                 "prefix sweep, storing forward sweep, dHidden sweep, row finish, "
-                                "scalars); the two sweeps are 91 % of it in the ncu launch list"},
+                                "scalars); the two sweeps are 90 % of it in the ncu launch list"},
         "step_tensor_frac": f_alg / (ms_step * 1e-3) / 1e12 / peaks["tflops"],
         "device_status": status,
         "plan": {"sm_count": caps.sm_count, "bwd_clusters_resident": caps.max_clusters_bwd,
@@ -607,8 +610,9 @@ def _vocab_parallel_c4(dist, par, make_config, make_weight, shape, dev, rank, wo
            "dtype": "bfloat16", "steps": steps, "ms_per_step": ms, "tokens_s": n / (ms * 1e-3),
            "tensor_frac": f_alg_gpu / (ms * 1e-3) / 1e12 / peaks["tflops"],
            "time_split_rank0": split, "dx_identical_on_all_ranks": bool((lo_chk == hi_chk).all()),
-           "note": "hidden 3584 takes the two-sweep path: a forward sweep keeps the logits as fp16 in "
-                   "HBM, head_dx_kernel turns them into dHidden (CTA pairs, 256 rows per W tile)"}
+           "note": "hidden 3584 takes the two-sweep path: a forward sweep keeps the softmax weights "
+                   "as bf16 in HBM, head_dx_kernel takes them by TMA and turns them into dHidden "
+                   "(CTA pairs, 256 rows per W tile)"}
     # parity: the oracle needs the whole W on the host; rank 0 rebuilds the other shards
     sub = torch.arange(0, n, n // 64)[:64]
     if rank == 0:
