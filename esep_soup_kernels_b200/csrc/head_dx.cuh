@@ -33,6 +33,13 @@
 // only help with the drain of the accumulators at the end of a run (TMEM lanes 32..63 can only be
 // read by warps with warp % 4 == 1); warp 5 also relays "tile ready" from the transform warps'
 // shared-memory counter to the leader's mbarrier. Every wait is bounded.
+//
+// kDirect (the default form of the path): the forward sweep has stored the weights themselves,
+// bf16 2^((z - m_ref - 40) log2 e) with the target's entry zero, so P needs no transform: warp 18
+// (which drains nothing) brings each step's tile in with two TMA boxes of 64 weights x 128 rows
+// per CTA, the layout above, and the sixteen warps only drain. The row's factor
+// 2^((m_ref + 40 - lse) log2 e) is applied by the row finish. Measured at 4 340 x 1536 x 151 936:
+// tensor pipe busy 92 % of the launch (72 % with the transform), 1.25 against 1.67 ms.
 #pragma once
 
 #include <algorithm>

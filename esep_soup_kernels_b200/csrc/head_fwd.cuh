@@ -1,5 +1,5 @@
 // Forward sweep of the LM head: logits tiles on tcgen05 tensor cores, softmax statistics in the
-// epilogue, logits never leave the SM.
+// epilogue; the statistics-only form never lets a logit leave the SM.
 //
 // Replaces, for all rows of x, the per-chunk pair
 //     torch.mm(x16[r0:r0+nr], W.t(), out=z)                    (solution/head/op.py:90)
@@ -20,6 +20,12 @@
 // only) + TMEM owner, warps 2..5 = epilogue (TMEM lane quadrant = warp_id % 4). The TMEM
 // accumulator is double buffered (2 x 256 columns) so the MMAs of tile k+1 overlap the epilogue
 // of tile k.
+//
+// kStore launches are the first of the training path's two sweeps (head_dx.cuh is the second):
+// they also keep one 16-bit value per logit in HBM - kStore 1: fp16 (z - m_ref) log2 e written
+// straight from the registers; kStore 2: the bf16 softmax weight 2^((z - m_ref - 40) log2 e), zero
+// at the target, which each epilogue warp stages in shared memory as a swizzled 64 x 32 box and
+// stores with one TMA instruction - and leave the target's entry out of the row sums.
 #pragma once
 
 #include <cuda_bf16.h>
