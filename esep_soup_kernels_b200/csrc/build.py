@@ -11,8 +11,9 @@ import sys
 CSRC = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(CSRC, "libesep_head.so")
 SOURCES = ["esep_head.cu"]
-HEADERS = ["sm100_ptx.cuh", "head_fwd.cuh", "head_bwd.cuh", "head_aux.cuh", "head_norm.cuh", "head_train.cuh",
-           os.path.join("..", "..", "include", "esep_head.h")]
+# every header of this directory is a dependency of the one translation unit
+HEADERS = sorted(f for f in os.listdir(CSRC) if f.endswith(".cuh")) + [
+    os.path.join("..", "..", "include", "esep_head.h")]
 
 
 def _nvcc():
