@@ -571,8 +571,10 @@ def test_warmup_from_a_worker_thread_and_no_one_time_work_afterwards():
         ws_keep.append(loss2)
     inits2, maps2 = counters()
     assert inits2 == inits
-    # the weight's maps are reused; only maps of freshly allocated scratch may be new
-    assert maps2 - maps1 <= 2 * 3
+    # the weight's maps are reused; only maps of freshly allocated scratch may be new (per call at
+    # most: the compact rows as the forward and as the guarded backward kernel read them, the
+    # stored weights as they are written and as they are read)
+    assert maps2 - maps1 <= 2 * 4
     assert torch.equal(loss.detach(), loss2.detach())
 
 
