@@ -19,20 +19,23 @@ As in the reference the input gradient is computed in the forward call when it i
 One C call (``esep_head_step``) does the whole of op.py:68-128 on the device and is a function of
 its arguments only: masks, the stable "rows with a loss first" order, the row counts and the
 work split of the kernels are all computed on the GPU, the host never waits for a count (the
-reference reads the number of live rows back on every call, op.py:116). Rows that need a
-gradient go through ONE pass over the vocabulary (logits computed once, statistics and dHidden
-from the same tiles); rows that only need statistics (ignored or zero-weight rows when there are
-many of them, every row of a call without gradient) go through a forward sweep. The logits are
-never written to memory (the 256-row chunk buffer of op.py:83-84 does not exist, so
-``chunk_rows`` is accepted and ignored) and stay fp32 in tensor memory instead of being rounded
-to fp16 (op.py:18, 90), so results sit closer to the fp32 oracle.
+reference reads the number of live rows back on every call, op.py:116). Every logit is computed
+once. Rows that need a gradient go through two sweeps over the vocabulary by default: a forward
+sweep that keeps the statistics and leaves the bf16 softmax weights in the workspace, and a
+dHidden sweep that reads them back by TMA (``set_training_path``: "stored_logits" keeps fp16
+logits instead, "single_pass" forms statistics and dHidden from the same tiles and writes
+nothing per logit). Rows that only need statistics (ignored or zero-weight rows when there are
+many of them, every row of a call without gradient) go through the forward sweep alone. The
+256-row chunk buffer of op.py:83-84 does not exist, so ``chunk_rows`` is accepted and ignored;
+the logits stay fp32 in tensor memory for the statistics instead of being rounded to fp16
+(op.py:18, 90), so results sit closer to the fp32 oracle.
 
-The single pass takes its softmax weights (bf16) relative to a per-row reference maximum from a
-vocabulary prefix; a row whose true maximum lies more than 115 above its prefix maximum raises a
-device flag and the library's guarded two-kernel path (forward sweep + recomputing backward
-sweep, queued behind the flag in the same call) replaces the results - no host synchronisation
-either way. For an fp16 model the dHidden GEMM reads a cached bf16 copy of the frozen weight
-(V*H*2 bytes of device memory per model). ``SINGLE_SWEEP = False`` makes calls with gradient use
+The default sweeps and the single pass take their softmax weights (bf16) relative to a per-row
+reference maximum from a vocabulary prefix; a row whose true maximum lies more than 115 above
+its prefix maximum raises a device flag and the library's guarded two-kernel path (forward
+sweep + recomputing backward sweep, queued behind the flag in the same call) replaces the
+results - no host synchronisation either way. For an fp16 model the dHidden GEMM of both reads
+a cached bf16 copy of the frozen weight (V*H*2 bytes of device memory per model). ``SINGLE_SWEEP = False`` makes calls with gradient use
 the two-kernel path directly.
 """
 
@@ -48,7 +51,7 @@ CHUNK_ROWS = 256
 G_SCALE = 1024.0
 VOCAB = 151936
 
-# Calls with gradient use the single pass (module docstring); False = forward sweep + backward
+# Calls with gradient use the library's step (module docstring); False = forward sweep + backward
 # sweep over all rows. A switch the caller sets, never something the library infers.
 SINGLE_SWEEP = True
 
@@ -248,8 +251,8 @@ def last_device_status(device=None):
 
 
 def last_call_used_stored_logits(device=None):
-    """True if the most recent call with gradient on the device took the two-sweep path (the
-    choice is made on the device for hidden sizes up to 1536). Synchronises (a test aid)."""
+    """True if the most recent call with gradient on the device took a two-sweep path (stored
+    weights or stored logits). Synchronises (a test aid)."""
     index = torch.cuda.current_device() if device is None else torch.device(device).index
     with _state_lock:
         ws = _last_workspace.get(index)
@@ -262,8 +265,9 @@ def last_call_used_stored_logits(device=None):
 
 
 def last_call_fell_back(device=None):
-    """True if the most recent single-pass call on the device raised its overflow flag, i.e. its
-    outputs came from the guarded two-kernel path. Synchronises (a test / monitoring aid)."""
+    """True if the most recent call on the device raised its overflow flag (single pass or stored
+    weights), i.e. its outputs came from the guarded two-kernel path. Synchronises (a test /
+    monitoring aid)."""
     device = torch.device("cuda" if device is None else device)
     index = torch.cuda.current_device() if device.index is None else device.index
     with _state_lock:

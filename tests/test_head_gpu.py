@@ -375,9 +375,9 @@ def test_two_sweeps_over_stored_logits_match_the_oracle(n, h, v, dtype, peak, pa
 
 
 def test_default_path_is_the_two_sweeps_and_both_paths_agree():
-    """Default: two sweeps over stored logits wherever they apply (hidden a multiple of 64), the
-    single pass otherwise or when asked for. Both paths agree to the rounding of their 16-bit
-    softmax weights."""
+    """Default: two sweeps (bf16 softmax weights kept between them) wherever they apply (hidden a
+    multiple of 64), the single pass otherwise or when asked for. Both paths agree to the rounding
+    of their 16-bit softmax weights."""
     from esep_soup_kernels_b200.head.op import last_call_used_stored_logits, set_training_path
 
     set_training_path("auto")
