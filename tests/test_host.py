@@ -45,6 +45,25 @@ def test_query_without_a_gpu_reports_an_error_not_a_crash():
     assert _lib.load().esep_head_workspace_bytes(128, 64, 1000, 0, 1) == 0
 
 
+def test_training_path_setting_is_host_state_with_four_values():
+    """0 auto, 1 single pass, 2 stored logits, 3 stored weights; the call returns the previous
+    value and refuses anything else. Without a GPU the path query answers 0 (no launch made)."""
+    lib = _lib.load()
+    first = lib.esep_head_set_training_path(0)
+    try:
+        prev = 0
+        for path in (1, 2, 3, 0):
+            assert lib.esep_head_set_training_path(path) == prev
+            prev = path
+        assert lib.esep_head_set_training_path(4) == _lib.ERR_BAD_ARG
+        assert lib.esep_head_set_training_path(-1) == _lib.ERR_BAD_ARG
+        assert lib.esep_head_set_training_path(0) == 0      # a refused value changes nothing
+        from esep_soup_kernels_b200.head.op import TRAINING_PATHS
+        assert sorted(TRAINING_PATHS.values()) == [0, 1, 2, 3]
+    finally:
+        lib.esep_head_set_training_path(first)
+
+
 @pytest.mark.parametrize("n,h,v", [(1, 64, 257), (77, 64, 1001), (4340, 1536, 151936),
                                     (16384, 1536, 151936), (32768, 3584, 19008), (4099, 1536, 151936)])
 def test_plan_covers_the_problem(n, h, v):
