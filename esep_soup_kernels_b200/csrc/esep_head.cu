@@ -899,9 +899,9 @@ struct StepLayout {
   int nhb_a, nhb_b;    // wide: accumulator blocks per producer / consumer CTA
   int rows_nhb;        // accumulator blocks per quarter of a pass, as the row-finish kernel sees it
   int pass_w;          // columns per pass = row stride of the partial dHidden pieces
-  bool stored;         // two sweeps: forward sweep that stores the logits, then head_dx_kernel
+  bool stored;         // two sweeps: forward sweep that keeps a 16-bit value per logit, then head_dx_kernel
   bool direct;         // ... stores the softmax weights themselves (bf16), head_dx_kernel<.., true>
-  size_t zpitch;       // elements per row of the stored logits
+  size_t zpitch;       // elements per row of that buffer
   size_t z_off, c2_off, partg_off, pieces_off;
   int part_cap;        // rows of the forward partial arrays
   size_t base_bytes;
@@ -1154,7 +1154,8 @@ int step_impl(const StepArgs& a) {
   float* part_g = reinterpret_cast<float*>(ws + t.partg_off);
   const size_t psg = t.part_stride / sizeof(float);
   if (need_grad && t.stored) {
-    // 4a. forward sweep over the compact rows [0, n_sweep) that keeps logit - m_ref as fp16
+    // 4a. forward sweep over the compact rows [0, n_sweep) that keeps the softmax weights as bf16
+    //     (direct) or logit - m_ref as fp16
     CUtensorMap tx, tw;
     if (make_tmap(&tx, xc, a.dtype, a.m, a.h, fwd::BK, fwd::BM) != ESEP_OK) return ESEP_ERR_CUDA;
     if (make_tmap(&tw, a.w, a.dtype, a.v, a.h, fwd::BK, fwd::BN / 2) != ESEP_OK)
@@ -1199,7 +1200,7 @@ int step_impl(const StepArgs& a) {
                                 s, tx, tw, tw, g);
     }
     if (st != ESEP_OK) return st;
-    // 4b. per-row constant of the softmax weights, 4c. dHidden from the stored logits
+    // 4b. per-row constant of the softmax weights, 4c. dHidden from the stored buffer
     float* kexp = reinterpret_cast<float*>(ws + t.c2_off);
     float* rscale = reinterpret_cast<float*>(ws + t.c2_off + align_up(static_cast<size_t>(m) * sizeof(float)));
     const unsigned rc_grid = static_cast<unsigned>(div_up(m, 128));
