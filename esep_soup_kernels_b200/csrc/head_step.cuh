@@ -290,8 +290,11 @@ __device__ __forceinline__ float merge_partial_records(const float* pm, const fl
   return big;
 }
 
+// 12 blocks per SM: the kernel waits for its loads (pieces, records), so resident warps count for
+// more than the 130 bytes of spills the 40-register cap costs (80 registers: 6 blocks per SM, 125 us
+// at 4 340 x 1536; capped: 85 us).
 template <int kFmt>
-__global__ void __launch_bounds__(128) head_step_rows_kernel(const StepRowsParams q) {
+__global__ void __launch_bounds__(128, 12) head_step_rows_kernel(const StepRowsParams q) {
   __shared__ float sh_f[4][4];
   __shared__ int sh_i[4];
   const int r = blockIdx.x;
