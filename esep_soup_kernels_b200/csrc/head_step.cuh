@@ -291,8 +291,9 @@ __device__ __forceinline__ float merge_partial_records(const float* pm, const fl
 }
 
 // 12 blocks per SM: the kernel waits for its loads (pieces, records), so resident warps count for
-// more than the 130 bytes of spills the 40-register cap costs (80 registers: 6 blocks per SM, 125 us
-// at 4 340 x 1536; capped: 85 us).
+// more than the 130 bytes of spills the 40-register cap costs (uncapped: 80 registers, 6 blocks per
+// SM, 125 us at 4 340 x 1536 with DRAM at 30 % of its bandwidth; capped, the whole step is 0.04 ms
+// shorter).
 template <int kFmt>
 __global__ void __launch_bounds__(128, 12) head_step_rows_kernel(const StepRowsParams q) {
   __shared__ float sh_f[4][4];
