@@ -45,6 +45,24 @@ def test_query_without_a_gpu_reports_an_error_not_a_crash():
     assert _lib.load().esep_head_workspace_bytes(128, 64, 1000, 0, 1) == 0
 
 
+def test_every_kernel_header_is_a_build_dependency():
+    """The library is one translation unit that includes every .cuh of csrc/: a header missing
+    from the dependency list would leave a stale library after an edit."""
+    import os
+    import re
+
+    from esep_soup_kernels_b200.csrc import build
+
+    csrc = os.path.dirname(build.__file__)
+    on_disk = {f for f in os.listdir(csrc) if f.endswith(".cuh")}
+    assert on_disk <= set(build.HEADERS)
+    included = set()
+    for name in ["esep_head.cu"] + sorted(on_disk):
+        with open(os.path.join(csrc, name)) as fh:
+            included |= set(re.findall(r'#include "([\w.]+\.cuh)"', fh.read()))
+    assert included <= on_disk and "head_dx.cuh" in included and "head_step.cuh" in included
+
+
 def test_training_path_setting_is_host_state_with_four_values():
     """0 auto, 1 single pass, 2 stored logits, 3 stored weights; the call returns the previous
     value and refuses anything else. Without a GPU the path query answers 0 (no launch made)."""
